@@ -1,0 +1,203 @@
+"""ctypes binding of libci_b200.so (the C ABI declared in include/comp_inference_b200.h).
+
+The shared library is the only compute backend of this package.  If it is
+missing or cannot be loaded, every operation raises; nothing falls back to
+PyTorch or to the CPU.
+"""
+import ctypes as C
+import os
+import weakref
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libci_b200.so")
+
+u8p = C.POINTER(C.c_uint8)
+u16p = C.POINTER(C.c_uint16)
+u32p = C.POINTER(C.c_uint32)
+u64p = C.POINTER(C.c_uint64)
+i64p = C.POINTER(C.c_int64)
+
+
+class TiledWeight(C.Structure):
+    """struct ci_tiled_weight"""
+    _fields_ = [("stream", C.c_void_p), ("states", C.c_void_p), ("tables", C.c_void_p), ("slot_map", C.c_void_p),
+                ("tile_offsets", C.c_void_p), ("tile_max_lens", C.c_void_p), ("mantissa", C.c_void_p),
+                ("lut", C.c_void_p), ("stream_len", C.c_uint64), ("K", C.c_uint32), ("N", C.c_uint32),
+                ("tile_h", C.c_uint32), ("tile_w", C.c_uint32), ("max_tile_len", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class DenseWeight(C.Structure):
+    """struct ci_dense_weight"""
+    _fields_ = [("stream", C.c_void_p), ("states", C.c_void_p), ("stream_sizes", C.c_void_p),
+                ("stream_offsets", C.c_void_p), ("tables", C.c_void_p), ("slot_map", C.c_void_p),
+                ("mantissa", C.c_void_p), ("lut", C.c_void_p), ("stream_len", C.c_uint64), ("K", C.c_uint32),
+                ("N", C.c_uint32), ("tile_h", C.c_uint32), ("tile_w", C.c_uint32)]
+
+
+# Every entry point of the header, with its argument types.  tests check this
+# table against the header and against the symbols the library exports.
+_V, _S = C.c_void_p, C.c_void_p
+SIGNATURES = {
+    "ci_abi_version": (C.c_int, []),
+    "ci_last_error": (C.c_char_p, []),
+    "ci_device_info": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ci_build_tables": (C.c_int, [_V, _V, _V, _V]),
+    "ci_prepare_lut": (C.c_int, [_V, _V, _V, _S]),
+    "ci_split_bf16": (C.c_int, [_V, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _V, _V, _V, _V, _S]),
+    "ci_histogram_u8": (C.c_int, [_V, C.c_uint64, _V, _S]),
+    "ci_normalize_freqs": (C.c_int, [_V, _V, _V]),
+    "ci_untile_mantissa": (C.c_int, [_V, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _V, _S]),
+    "ci_encode_tiled_sizes": (C.c_int, [_V, C.c_uint32, C.c_uint32, _V, _V, C.c_uint32, C.c_uint32, _V, _V, _V, _V,
+                                        u64p, _S]),
+    "ci_encode_tiled_write": (C.c_int, [_V, C.c_uint32, C.c_uint32, _V, _V, C.c_uint32, C.c_uint32, _V, _V, _V, _V,
+                                        C.c_uint64, _S]),
+    "ci_encode_dense_sizes": (C.c_int, [_V, C.c_uint32, C.c_uint32, _V, _V, C.c_uint32, C.c_uint32, _V, _V, _V,
+                                        u64p, _S]),
+    "ci_encode_dense_write": (C.c_int, [_V, C.c_uint32, C.c_uint32, _V, _V, C.c_uint32, C.c_uint32, _V, _V,
+                                        C.c_uint64, _S]),
+    "ci_decode_plane": (C.c_int, [C.POINTER(TiledWeight), _V, _S]),
+    "ci_decode_bf16": (C.c_int, [C.POINTER(TiledWeight), _V, _S]),
+    "ci_decode_plane_dense": (C.c_int, [C.POINTER(DenseWeight), _V, _S]),
+    "ci_decode_bf16_dense": (C.c_int, [C.POINTER(DenseWeight), _V, _S]),
+    "ci_linear_workspace_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "ci_linear": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V, C.c_size_t,
+                            C.c_uint32, _S]),
+    "ci_linear_transposed": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V,
+                                       C.c_size_t, _S]),
+    "ci_embedding": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_uint64, _V, C.c_int64, _S]),
+    "ci_linear_dense": (C.c_int, [C.POINTER(DenseWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V,
+                                  C.c_size_t, C.c_uint32, _S]),
+    "ci_embedding_dense": (C.c_int, [C.POINTER(DenseWeight), _V, C.c_uint64, _V, C.c_int64, _S]),
+    "ci_decode_legacy": (C.c_int, [_V, C.c_uint64, _V, _V, C.c_uint32, C.c_uint64, _V, _V, _V, _S]),
+}
+
+_lib = None
+
+
+def load():
+    """Returns the loaded library; raises RuntimeError if it is not there."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python comp_inference_b200/csrc/build.py` "
+            "(needs nvcc with sm_100a support). This package has no other backend.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError here = library older than the header
+        fn.restype = res
+        fn.argtypes = args
+    if lib.ci_abi_version() != 1:
+        raise RuntimeError(f"libci_b200.so has ABI version {lib.ci_abi_version()}, expected 1")
+    _lib = lib
+    return lib
+
+
+def check(rc):
+    if rc != 0:
+        msg = load().ci_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"comp_inference_b200: {msg} (code {rc})")
+
+
+def stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def require_cuda(t, name):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    return t
+
+
+def as_u32(t, name):
+    """32-bit metadata arrives as uint32 or int32 (the reference casts back and forth); same bits."""
+    if t.dtype not in (torch.uint32, torch.int32):
+        raise RuntimeError(f"{name} must be uint32 or int32, got {t.dtype}")
+    return t.contiguous()
+
+
+def as_u8(t, name):
+    if t.dtype != torch.uint8:
+        raise RuntimeError(f"{name} must be uint8, got {t.dtype}")
+    return t.contiguous()
+
+
+# ---- prepared decode tables, one per (tables, slot_map) pair -----------------
+_lut_cache = {}
+
+
+def prepared_lut(tables, slot_map):
+    """Device uint32[4096] merged decode table for this tables/slot_map pair (cached per tensor object)."""
+    key = (tables.data_ptr(), slot_map.data_ptr())
+    hit = _lut_cache.get(key)
+    if hit is not None:
+        ref_t, ref_s, ver, lut = hit
+        if ref_t() is tables and ref_s() is slot_map and ver == (tables._version, slot_map._version):
+            return lut
+    lut = torch.empty(4096, dtype=torch.int32, device=tables.device)
+    check(load().ci_prepare_lut(ptr(tables), ptr(slot_map), ptr(lut), stream()))
+    if len(_lut_cache) > 4096:
+        _lut_cache.clear()
+    _lut_cache[key] = (weakref.ref(tables), weakref.ref(slot_map), (tables._version, slot_map._version), lut)
+    return lut
+
+
+# ---- split-K workspace: one zero-initialised buffer per device, grown on demand
+_workspaces = {}
+
+
+def workspace(device, nbytes):
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def tiled_weight(stream_t, states, tables, slot_map, tile_offsets, tile_max_lens, mantissa, K, N, th, tw, lut=None,
+                 keep=None):
+    """Fills a ci_tiled_weight from CUDA tensors; returns (struct, tensors that must stay alive)."""
+    require_cuda(stream_t, "compressed stream")
+    st = as_u8(stream_t, "compressed stream")
+    sts = as_u32(require_cuda(states, "states"), "states")
+    tb = as_u32(require_cuda(tables, "tables"), "tables")
+    sm = as_u8(require_cuda(slot_map, "slot_map"), "slot_map")
+    off = as_u32(require_cuda(tile_offsets, "tile_offsets"), "tile_offsets")
+    ml = as_u32(require_cuda(tile_max_lens, "tile_max_lens"), "tile_max_lens")
+    man = as_u8(require_cuda(mantissa, "mantissas"), "mantissas") if mantissa is not None else None
+    tiles = -(-K // th) * -(-N // tw)
+    if sts.numel() != tiles * 2 * tw:
+        raise ValueError(f"Initial states size mismatch. Expected {tiles * 2 * tw}")     # rans_triton.py:141-144
+    if off.numel() != tiles or ml.numel() != tiles:
+        raise ValueError(f"tile_offsets / tile_max_lens must have {tiles} entries")
+    if man is not None and man.numel() < tiles * th * tw:
+        raise ValueError(f"mantissa plane has {man.numel()} bytes, {tiles * th * tw} expected")
+    if lut is None:
+        lut = prepared_lut(tb, sm) if (tb is tables and sm is slot_map) else None
+    w = TiledWeight(ptr(st), ptr(sts), ptr(tb), ptr(sm), ptr(off), ptr(ml), ptr(man), ptr(lut), st.numel(),
+                    K, N, th, tw, 0, 0)
+    return w, (st, sts, tb, sm, off, ml, man, lut, keep)
+
+
+def dense_weight(stream_t, states, sizes, offsets, tables, slot_map, mantissa, K, N, th, tw):
+    require_cuda(stream_t, "compressed stream")
+    st = as_u8(stream_t, "compressed stream")
+    sts = as_u32(require_cuda(states, "states"), "states")
+    sz = as_u32(require_cuda(sizes, "stream_sizes"), "stream_sizes")
+    off = as_u32(require_cuda(offsets, "stream_offsets"), "stream_offsets")
+    tb = as_u32(require_cuda(tables, "tables"), "tables")
+    sm = as_u8(require_cuda(slot_map, "slot_map"), "slot_map")
+    man = as_u8(require_cuda(mantissa, "mantissas"), "mantissas") if mantissa is not None else None
+    n = -(-K // th) * -(-N // tw) * tw
+    if sts.numel() != n or sz.numel() != n or off.numel() != n:
+        raise ValueError(f"dense layout needs {n} states / sizes / offsets")
+    lut = prepared_lut(tb, sm) if (tb is tables and sm is slot_map) else None
+    w = DenseWeight(ptr(st), ptr(sts), ptr(sz), ptr(off), ptr(tb), ptr(sm), ptr(man), ptr(lut), st.numel(), K, N, th, tw)
+    return w, (st, sts, sz, off, tb, sm, man, lut)

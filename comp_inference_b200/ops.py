@@ -1,0 +1,173 @@
+"""The reference's Python ops, same names and keyword arguments, on the CUDA
+kernels of libci_b200.so.  (The names still say "triton" because they are the
+public API of the reference; nothing here is Triton.)
+
+    rans_decomp_triton_tiled                  comp_inference/rans_triton.py:122-168
+    fused_rans_linear_triton                  comp_inference/linear_triton.py:229-314
+    fused_rans_linear_transposed_triton       comp_inference/transposed_linear_triton.py:361-435
+    fused_rans_embedding_triton               comp_inference/embedding_triton.py:278-330
+    *_uncoalesced variants                    linear_triton.py:1189-1265, embedding_triton.py:431-483
+    triton_matmul                             comp_inference/triton_gemm.py:324-337
+
+All tensor arguments must already be CUDA tensors; inputs are borrowed for the
+call, outputs are fresh tensors or the caller's ``out``.  Everything is queued on
+the current torch CUDA stream and nothing synchronises.
+"""
+import torch
+
+from . import _lib
+
+
+def _check_x(x, K):
+    if x.dtype != torch.bfloat16:
+        raise RuntimeError(f"activations must be bfloat16, got {x.dtype}")
+    _lib.require_cuda(x, "x")
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    return x2
+
+
+def _bias(bias, n):
+    if bias is None:
+        return None
+    if bias.dtype != torch.bfloat16 or bias.numel() != n:
+        raise RuntimeError("bias must be bfloat16 with one entry per output feature")
+    return bias.contiguous()
+
+
+def rans_decomp_triton_tiled(compressed_streams, initial_states, tables, slot_map, output_shape, tile_offsets,
+                             tile_max_lens, tile_k=1024, tile_n=32):
+    """Exponent plane uint8 [K,N] of a tiled stream."""
+    K, N = int(output_shape[0]), int(output_shape[1])
+    w, keep = _lib.tiled_weight(compressed_streams, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
+                                None, K, N, int(tile_k), int(tile_n))
+    out = torch.empty((K, N), device=compressed_streams.device, dtype=torch.uint8)
+    _lib.check(_lib.load().ci_decode_plane(w, _lib.ptr(out), _lib.stream()))
+    return out
+
+
+def rans_decompress_bf16(compressed_streams, initial_states, tables, slot_map, weight_shape, tile_offsets,
+                         tile_max_lens, tile_k, tile_n, mantissas):
+    """Whole weight as bfloat16 [K,N] in one kernel: the decode + uninterleave + reconstruct
+    chain of rans_decompress_module_weight_bf16 (comp_inference/comp_inference.py:633-711)."""
+    K, N = int(weight_shape[0]), int(weight_shape[1])
+    w, keep = _lib.tiled_weight(compressed_streams, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
+                                mantissas, K, N, int(tile_k), int(tile_n))
+    out = torch.empty((K, N), device=compressed_streams.device, dtype=torch.bfloat16)
+    _lib.check(_lib.load().ci_decode_bf16(w, _lib.ptr(out), _lib.stream()))
+    return out
+
+
+def _linear_call(w, x2, M, n_out, bias, out, split_k, transposed):
+    dev = x2.device
+    lib = _lib.load()
+    y = out.view(M, n_out) if out is not None else torch.empty((M, n_out), device=dev, dtype=torch.bfloat16)
+    if y.dtype != torch.bfloat16 or y.stride(1) != 1:
+        raise RuntimeError("out must be a bfloat16 tensor with unit inner stride")
+    nbytes = lib.ci_linear_workspace_bytes(M, n_out, 0, 0)
+    ws = _lib.workspace(dev, nbytes)
+    b = _bias(bias, n_out)
+    if transposed:
+        _lib.check(lib.ci_linear_transposed(w, _lib.ptr(x2), x2.stride(0), M, _lib.ptr(b), _lib.ptr(y), y.stride(0),
+                                            _lib.ptr(ws), ws.numel(), _lib.stream()))
+    else:
+        _lib.check(lib.ci_linear(w, _lib.ptr(x2), x2.stride(0), M, _lib.ptr(b), _lib.ptr(y), y.stride(0),
+                                 _lib.ptr(ws), ws.numel(), int(split_k), _lib.stream()))
+    return y
+
+
+def fused_rans_linear_triton(x, compressed_data, initial_states, tables, slot_map, weight_shape, tile_offsets,
+                             tile_max_lens, tile_k, tile_n, mantissas, accum_block_size=32, bias=None, out=None,
+                             SPLIT_K=8, workspace=None):
+    """y[..., N] = x[..., K] . W[K, N] (+ bias) with W decoded on the fly.
+
+    ``accum_block_size`` and ``workspace`` are accepted for source compatibility: blocking is internal,
+    and split-K partials live in this package's own fp32 workspace (the reference's is a bf16 buffer
+    of another size).  ``SPLIT_K`` is honoured up to 16; 0 lets the library choose.
+    """
+    K, N = int(weight_shape[0]), int(weight_shape[1])
+    x2 = _check_x(x, K)
+    M = x2.shape[0]
+    w, keep = _lib.tiled_weight(compressed_data, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
+                                mantissas, K, N, int(tile_k), int(tile_n))
+    y = _linear_call(w, x2, M, N, bias, out, SPLIT_K, False)
+    return out if out is not None else y.view(*x.shape[:-1], N)
+
+
+def fused_rans_linear_transposed_triton(x, compressed_data, initial_states, tables, slot_map, weight_shape,
+                                        tile_offsets, tile_max_lens, tile_k, tile_n, mantissas, workspace=None,
+                                        bias=None, out=None, SPLIT_K=8):
+    """y[..., V] = x[..., H] . W[V, H]^T for a weight stored [V, H] (LM head / tied embedding)."""
+    V, H = int(weight_shape[0]), int(weight_shape[1])
+    x2 = _check_x(x, H)
+    M = x2.shape[0]
+    w, keep = _lib.tiled_weight(compressed_data, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
+                                mantissas, V, H, int(tile_k), int(tile_n))
+    y = _linear_call(w, x2, M, V, bias, out, 0, True)
+    return out if out is not None else y.view(*x.shape[:-1], V)
+
+
+def fused_rans_embedding_triton(x, compressed_data, initial_states, tables, slot_map, weight_shape, tile_offsets,
+                                tile_max_lens, tile_k, tile_n, mantissas, out=None):
+    """out[..., :] = W[x[...], :]; ids outside [0, K) give zero rows."""
+    K, N = int(weight_shape[0]), int(weight_shape[1])
+    _lib.require_cuda(x, "x")
+    ids = x.reshape(-1).to(torch.int64).contiguous()
+    n = ids.numel()
+    w, keep = _lib.tiled_weight(compressed_data, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
+                                mantissas, K, N, int(tile_k), int(tile_n))
+    o = out.view(n, N) if out is not None else torch.empty((n, N), device=x.device, dtype=torch.bfloat16)
+    if o.dtype != torch.bfloat16 or (n > 0 and o.stride(1) != 1):
+        raise RuntimeError("out must be a bfloat16 tensor with unit inner stride")
+    _lib.check(_lib.load().ci_embedding(w, _lib.ptr(ids), n, _lib.ptr(o), o.stride(0) if n else N, _lib.stream()))
+    return o.view(*x.shape, N)
+
+
+# ---- dense ("uncoalesced") layout ------------------------------------------------
+
+def rans_decomp_uncoalesced(compressed_streams, initial_states, tables, slot_map, output_shape, stream_offsets,
+                            stream_sizes, tile_k, tile_n):
+    """Exponent plane of a dense-layout stream (no reference counterpart as a stand-alone op)."""
+    K, N = int(output_shape[0]), int(output_shape[1])
+    w, keep = _lib.dense_weight(compressed_streams, initial_states, stream_sizes, stream_offsets, tables, slot_map,
+                                None, K, N, int(tile_k), int(tile_n))
+    out = torch.empty((K, N), device=compressed_streams.device, dtype=torch.uint8)
+    _lib.check(_lib.load().ci_decode_plane_dense(w, _lib.ptr(out), _lib.stream()))
+    return out
+
+
+def fused_rans_linear_triton_uncoalesced(x, compressed_data, initial_states, tables, slot_map, weight_shape,
+                                         stream_offsets, stream_sizes, tile_k, tile_n, mantissas,
+                                         accum_block_size=32, bias=None, out=None, SPLIT_K=8, workspace=None):
+    K, N = int(weight_shape[0]), int(weight_shape[1])
+    x2 = _check_x(x, K)
+    M = x2.shape[0]
+    w, keep = _lib.dense_weight(compressed_data, initial_states, stream_sizes, stream_offsets, tables, slot_map,
+                                mantissas, K, N, int(tile_k), int(tile_n))
+    lib = _lib.load()
+    y = out.view(M, N) if out is not None else torch.empty((M, N), device=x2.device, dtype=torch.bfloat16)
+    ws = _lib.workspace(x2.device, lib.ci_linear_workspace_bytes(M, N, 0, 0))
+    b = _bias(bias, N)
+    _lib.check(lib.ci_linear_dense(w, _lib.ptr(x2), x2.stride(0), M, _lib.ptr(b), _lib.ptr(y), y.stride(0),
+                                   _lib.ptr(ws), ws.numel(), int(SPLIT_K), _lib.stream()))
+    return out if out is not None else y.view(*x.shape[:-1], N)
+
+
+def fused_rans_embedding_triton_uncoalesced(x, compressed_data, initial_states, tables, slot_map, weight_shape,
+                                            stream_offsets, stream_sizes, tile_k, tile_n, mantissas, out=None):
+    K, N = int(weight_shape[0]), int(weight_shape[1])
+    ids = _lib.require_cuda(x, "x").reshape(-1).to(torch.int64).contiguous()
+    n = ids.numel()
+    w, keep = _lib.dense_weight(compressed_data, initial_states, stream_sizes, stream_offsets, tables, slot_map,
+                                mantissas, K, N, int(tile_k), int(tile_n))
+    o = out.view(n, N) if out is not None else torch.empty((n, N), device=x.device, dtype=torch.bfloat16)
+    _lib.check(_lib.load().ci_embedding_dense(w, _lib.ptr(ids), n, _lib.ptr(o), o.stride(0) if n else N,
+                                              _lib.stream()))
+    return o.view(*x.shape, N)
+
+
+def triton_matmul(a, b):
+    """Dense bf16 matmul on an already decompressed [K,N] weight (comp_inference/triton_gemm.py:324-337).
+    A plain library GEMM: nothing compressed is involved, so this is torch.matmul."""
+    return torch.matmul(a, b)

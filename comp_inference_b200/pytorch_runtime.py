@@ -1,0 +1,147 @@
+"""Module wrappers over the compressed buffers and the Hugging Face model patcher
+(the reference's comp_inference/pytorch_runtime.py:386-642), with the same class
+names, constructor arguments and buffer names, so a saved package loads unchanged.
+
+Buffers are device-resident; the per-forward ``.to(device)`` calls of the
+reference (its CPU "on-demand offloading", pytorch_runtime.py:440-459) are gone
+because there is no CPU path here.
+"""
+import torch
+import torch.nn as nn
+
+from . import _lib
+from .ops import (fused_rans_embedding_triton, fused_rans_linear_transposed_triton, fused_rans_linear_triton)
+
+_BUFFERS = (("rans_exp_stream", torch.uint8), ("rans_exp_states", torch.uint32), ("rans_exp_tables", torch.uint32),
+            ("rans_exp_slot_map", torch.uint8), ("rans_exp_tile_offsets", torch.uint32),
+            ("rans_exp_tile_max_lens", torch.uint32), ("rans_man_raw", torch.uint8), ("rans_info", torch.int32))
+
+
+class RansWorkspace:
+    """Kept for source compatibility (pytorch_runtime.py:386-394).  Split-K partials of this package
+    live in an internal fp32 buffer per device; this returns a view of that buffer's storage size-wise
+    compatible placeholder so callers that pass ``workspace=`` keep working."""
+    _buffer = None
+
+    @classmethod
+    def get_workspace(cls, M, N, split_k, device):
+        elements = max(M * N * split_k, 1)
+        if cls._buffer is None or cls._buffer.numel() < elements or cls._buffer.device != torch.device(device):
+            cls._buffer = torch.zeros(elements * 2, device=device, dtype=torch.bfloat16)
+        return cls._buffer[:elements].view(split_k, M, N)
+
+
+class _RansBase(nn.Module):
+    def _register(self):
+        for name, dt in _BUFFERS:
+            self.register_buffer(name, torch.empty(0, dtype=dt))
+
+    def load_compressed(self, c):
+        """Adopts the tensors of a dict produced by comp_inference.compress_weight_cuda (or a saved package)."""
+        for name, _ in _BUFFERS:
+            if name in c:
+                setattr(self, name, c[name])
+        return self
+
+    def _args(self):
+        return dict(compressed_data=self.rans_exp_stream, initial_states=self.rans_exp_states,
+                    tables=self.rans_exp_tables, slot_map=self.rans_exp_slot_map,
+                    tile_offsets=self.rans_exp_tile_offsets, tile_max_lens=self.rans_exp_tile_max_lens,
+                    tile_k=self.tile_k, tile_n=self.tile_n, mantissas=self.rans_man_raw)
+
+
+class RansLinear(_RansBase):
+    """nn.Linear replacement; weight stored compressed as [K=in, N=out] (pytorch_runtime.py:397-459)."""
+
+    def __init__(self, in_features: int, out_features: int, tile_k: int = 1024, tile_n: int = 32, split_k: int = 1,
+                 has_bias: bool = False):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.tile_k, self.tile_n, self.split_k = tile_k, tile_n, split_k
+        self._register()
+        if has_bias:
+            self.register_buffer("bias", torch.empty(out_features, dtype=torch.bfloat16))
+        else:
+            self.bias = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return fused_rans_linear_triton(x=x, weight_shape=(self.in_features, self.out_features), bias=self.bias,
+                                        SPLIT_K=self.split_k if self.split_k > 1 else 0, **self._args())
+
+
+class RansLMHead(_RansBase):
+    """LM head whose weight is stored [V=out, H=in] (pytorch_runtime.py:462-505)."""
+
+    def __init__(self, in_features: int, out_features: int, tile_k: int = 1024, tile_n: int = 32):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.tile_k, self.tile_n = tile_k, tile_n
+        self._register()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return fused_rans_linear_transposed_triton(x=x, weight_shape=(self.out_features, self.in_features),
+                                                   bias=None, SPLIT_K=1, **self._args())
+
+
+class RansEmbedding(_RansBase):
+    """nn.Embedding replacement; table stored [V, H] (pytorch_runtime.py:508-549)."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, tile_k: int = 1024, tile_n: int = 32):
+        super().__init__()
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.tile_k, self.tile_n = tile_k, tile_n
+        self._register()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return fused_rans_embedding_triton(x=x, weight_shape=(self.num_embeddings, self.embedding_dim),
+                                           **self._args())
+
+
+def patch_model(model, state_dict, layer_configs=None, default_th=1024, default_tw=32, split_k=1):
+    """Swaps every module that has ``<name>.rans_exp_stream`` in state_dict for its Rans* counterpart and
+    assigns all tensors by name (the body of load_compressed_model_with_auto_model, pytorch_runtime.py:572-637)."""
+    layer_configs = layer_configs or {}
+    replacements = []
+    for name, module in model.named_modules():
+        if "lm_head" in name or isinstance(module, (RansLinear, RansEmbedding, RansLMHead)):
+            continue
+        if f"{name}.rans_exp_stream" not in state_dict:
+            continue
+        th = layer_configs.get(name, {}).get("tile_height", default_th)
+        tw = layer_configs.get(name, {}).get("tile_width", default_tw)
+        if isinstance(module, nn.Linear):
+            replacements.append((name, RansLinear(module.in_features, module.out_features, th, tw, split_k,
+                                                  module.bias is not None)))
+        elif isinstance(module, nn.Embedding):
+            replacements.append((name, RansEmbedding(module.num_embeddings, module.embedding_dim, th, tw)))
+    for name, new_layer in replacements:
+        parent_name, _, child = name.rpartition(".")
+        parent = model.get_submodule(parent_name) if parent_name else model
+        setattr(parent, child, new_layer)
+    if hasattr(model, "lm_head") and "lm_head.rans_exp_stream" in state_dict:
+        th = layer_configs.get("lm_head", {}).get("tile_height", default_th)
+        tw = layer_configs.get("lm_head", {}).get("tile_width", default_tw)
+        model.lm_head = RansLMHead(model.lm_head.in_features, model.lm_head.out_features, tile_k=th, tile_n=tw)
+    targets = dict(model.named_buffers())
+    targets.update(dict(model.named_parameters()))
+    for name, target in targets.items():
+        if name in state_dict:
+            target.data = state_dict[name].contiguous()
+    return model
+
+
+def load_compressed_model_with_auto_model(model_id: str, safetensors_path: str, split_k: int = 1,
+                                          compile_model: bool = False):
+    """Loads the dense Hugging Face model, swaps in the compressed modules, moves everything to the GPU
+    (pytorch_runtime.py:552-642).  ``compile_model`` is accepted and ignored: there is no tracing compiler here."""
+    from safetensors.torch import load_file
+    from transformers import AutoModelForCausalLM
+    _lib.load()
+    model = AutoModelForCausalLM.from_pretrained(model_id, torch_dtype=torch.bfloat16, trust_remote_code=True)
+    quant = getattr(model.config, "quantization_config", {}) or {}
+    if not isinstance(quant, dict):
+        quant = quant.to_dict() if hasattr(quant, "to_dict") else dict(quant)
+    state_dict = load_file(safetensors_path, device="cpu")
+    patch_model(model, state_dict, quant.get("layer_configs", {}), quant.get("default_tile_height", 1024),
+                quant.get("default_tile_width", 32), split_k)
+    return model.cuda()

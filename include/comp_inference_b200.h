@@ -1,0 +1,226 @@
+/*
+ * comp_inference_b200 -- C ABI of the compressed-weight hot path (sm_100a).
+ *
+ * This is the boundary a binding of the reference project would attach to in
+ * place of its own extension module (src/python_bindings.cpp) and of the Triton
+ * kernels its Python ops launch.  Plain pointers and sizes only; every pointer
+ * named "d_*" or living inside ci_tiled_weight is DEVICE memory, everything
+ * else is host memory.  All launches go to the cudaStream_t passed as
+ * `stream` (void* here so the header needs no CUDA include) and do not
+ * synchronise unless stated.
+ *
+ * Return value: 0 on success, a negative CI_E_* code otherwise; the message of
+ * the last failure on the calling thread is returned by ci_last_error().
+ * There is no CPU fallback anywhere behind this header.
+ *
+ * File:line citations name the reference interface an entry point replaces
+ * (paths relative to the reference project root).
+ */
+#ifndef COMP_INFERENCE_B200_H
+#define COMP_INFERENCE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CI_ABI_VERSION 1
+
+#define CI_OK 0
+#define CI_E_INVALID (-1)   /* bad argument (shape, tile size, null pointer, alignment) */
+#define CI_E_CUDA (-2)      /* a CUDA runtime call failed; ci_last_error() has its text   */
+#define CI_E_OVERFLOW (-3)  /* compressed stream would exceed the format's 32-bit offsets */
+#define CI_E_WORKSPACE (-4) /* caller-provided workspace too small                         */
+#define CI_E_DEVICE (-5)    /* a kernel reported an error through its status word         */
+
+typedef void *ci_stream_t; /* cudaStream_t */
+
+/*
+ * One compressed tensor W[K,N] in the reference's "coalesced ILP2" layout
+ * (produced by RansManager.compress_tiled, src/python_bindings.cpp:302-347;
+ * stored as rans_exp_* / rans_man_raw by comp_inference/rans_saving.py:383-475;
+ * held by RansLinear / RansLMHead / RansEmbedding,
+ * comp_inference/pytorch_runtime.py:414-425).
+ *
+ * Tile t = tk*ceil(N/tile_w) + tn covers rows [tk*tile_h, +tile_h) and columns
+ * [tn*tile_w, +tile_w).  It owns 2*tile_w streams: t*2*tile_w + c codes the top
+ * half rows of column c, + tile_w the bottom half.  Its bytes start at
+ * tile_offsets[t] and form a row-major [tile_max_lens[t]][2*tile_w] matrix, one
+ * column per stream, each stream bottom-aligned.  mantissa is the raw
+ * sign+mantissa plane re-tiled to [tk][tn][tile_h][tile_w].
+ */
+typedef struct ci_tiled_weight {
+    const uint8_t *stream;         /* rans_exp_stream          [stream_len]            */
+    const uint32_t *states;        /* rans_exp_states          [tiles * 2 * tile_w]    */
+    const uint32_t *tables;        /* rans_exp_tables          [256]  freq | cdf << 16 */
+    const uint8_t *slot_map;       /* rans_exp_slot_map        [4096]                  */
+    const uint32_t *tile_offsets;  /* rans_exp_tile_offsets    [tiles]                 */
+    const uint32_t *tile_max_lens; /* rans_exp_tile_max_lens   [tiles]                 */
+    const uint8_t *mantissa;       /* rans_man_raw             [tiles * tile_h * tile_w]; may be NULL for ci_decode_plane */
+    const uint32_t *lut;           /* optional: [4096] from ci_prepare_lut, or NULL (kernels then build it themselves) */
+    uint64_t stream_len;           /* bytes in stream                                   */
+    uint32_t K, N;                 /* logical matrix                                    */
+    uint32_t tile_h, tile_w;       /* tile_h % 16 == 0; tile_w in {8,16,32,64,128}      */
+    uint32_t max_tile_len;         /* max over tile_max_lens if known, else 0           */
+    uint32_t reserved;
+} ci_tiled_weight;
+
+/* Same tensor in the dense ("uncoalesced") layout: one stream per tile column,
+ * streams concatenated (RansManager.compress_tiled_uncoalesced,
+ * src/python_bindings.cpp:349-397; rans_exp_stream_offsets in rans_saving.py). */
+typedef struct ci_dense_weight {
+    const uint8_t *stream;
+    const uint32_t *states;         /* [tiles * tile_w] */
+    const uint32_t *stream_sizes;   /* [tiles * tile_w] */
+    const uint32_t *stream_offsets; /* [tiles * tile_w] */
+    const uint32_t *tables;
+    const uint8_t *slot_map;
+    const uint8_t *mantissa;
+    const uint32_t *lut;
+    uint64_t stream_len;
+    uint32_t K, N, tile_h, tile_w;
+} ci_dense_weight;
+
+int ci_abi_version(void);
+const char *ci_last_error(void);
+
+/* Device properties the host side sizes launches with (SM count etc.); fills
+ * sm_count / max dynamic shared memory per block of the current device. */
+int ci_device_info(int *sm_count, int *max_smem_per_block);
+
+/* ---- tables ------------------------------------------------------------ */
+
+/* Host.  Packed {freq,cdf} table and slot->symbol map from 12-bit frequencies.
+ * Replaces the table packing of src/cuda/rans_host.cuh:476-488. */
+int ci_build_tables(const uint16_t *freqs, const uint16_t *cdf, uint32_t *tables, uint8_t *slot_map);
+
+/* Device.  Merges tables + slot_map into the 4096-entry decode table the
+ * kernels keep in shared memory: entry[slot] = bias | freq << 12 | sym << 24,
+ * bias = slot - cdf[sym].  (The reference's decoders do two dependent global
+ * lookups per symbol instead: comp_inference/rans_triton.py:95-105.) */
+int ci_prepare_lut(const uint32_t *d_tables, const uint8_t *d_slot_map, uint32_t *d_lut, ci_stream_t stream);
+
+/* ---- bf16 split / merge, histogram ------------------------------------- */
+
+/* Device.  bf16 bits [K,N] -> exponent plane u8 [K,N], sign+mantissa bytes
+ * re-tiled to [tk][tn][tile_h][tile_w] (zero padded; tile_h = 0 keeps the plain
+ * [K,N] order), and 256-bin histograms of both byte planes (u64[256] each,
+ * zeroed by the call).  Replaces extract_exp_and_mantissa + interleave_mantissas
+ * + the bincount of get_rans_lut (comp_inference/comp_inference.py:10-32, 35-64,
+ * 190-191).  Any output may be NULL. */
+int ci_split_bf16(const uint16_t *d_w, uint32_t K, uint32_t N, uint32_t tile_h, uint32_t tile_w,
+                  uint8_t *d_exp_plane, uint8_t *d_mantissa_tiled, uint64_t *d_exp_hist256,
+                  uint64_t *d_man_hist256, ci_stream_t stream);
+
+/* Device.  256-bin histogram of a byte array (the np.bincount of get_rans_lut,
+ * comp_inference/comp_inference.py:190-191); d_hist256 is zeroed by the call. */
+int ci_histogram_u8(const uint8_t *d_data, uint64_t n, uint64_t *d_hist256, ci_stream_t stream);
+
+/* Host.  12-bit frequency table from a 256-bin histogram with exactly the
+ * rounding and fix-up rules of get_rans_lut (comp_inference/comp_inference.py:193-239). */
+int ci_normalize_freqs(const uint64_t *hist256, uint16_t *freqs, uint16_t *cdf);
+
+/* Device.  Inverse re-tiling of the mantissa plane (uninterleave_mantissas,
+ * comp_inference/comp_inference.py:67-93). */
+int ci_untile_mantissa(const uint8_t *d_tiled, uint32_t K, uint32_t N, uint32_t tile_h, uint32_t tile_w,
+                       uint8_t *d_plane, ci_stream_t stream);
+
+/* ---- encoder ------------------------------------------------------------ */
+
+/* GPU encoder, ILP2 tiled layout, in two steps so that the caller owns every
+ * allocation.  Replaces RansManager::compress_tiled_ilp2 (src/cuda/rans_ops.cu:205-410:
+ * kernel src/cuda/rans_kernels.cuh:76-188 plus the single-threaded host repack
+ * :328-370); the bytes are written straight into their final, packed place.
+ *
+ * Step 1 fills d_states, d_sizes [tiles*2*tile_w], d_tile_max_lens and
+ * d_tile_offsets [tiles], returns the stream length in *stream_len and
+ * SYNCHRONISES the stream (the caller needs the number to allocate).
+ * Step 2 writes d_stream[stream_len] (the call zero-fills it first).
+ * freqs / cdf are host arrays of 256.  tile_h % 16 == 0 is required
+ * (src/cuda/rans_host.cuh:440-445). */
+int ci_encode_tiled_sizes(const uint8_t *d_plane, uint32_t K, uint32_t N, const uint16_t *freqs, const uint16_t *cdf,
+                          uint32_t tile_h, uint32_t tile_w, uint32_t *d_states, uint32_t *d_sizes,
+                          uint32_t *d_tile_offsets, uint32_t *d_tile_max_lens, uint64_t *stream_len,
+                          ci_stream_t stream);
+int ci_encode_tiled_write(const uint8_t *d_plane, uint32_t K, uint32_t N, const uint16_t *freqs, const uint16_t *cdf,
+                          uint32_t tile_h, uint32_t tile_w, const uint32_t *d_sizes, const uint32_t *d_tile_offsets,
+                          const uint32_t *d_tile_max_lens, uint8_t *d_stream, uint64_t stream_len, ci_stream_t stream);
+
+/* Dense layout encoder (RansManager::compress_tiled_uncoalesced,
+ * src/cuda/rans_ops.cu:74-203; kernel src/cuda/rans_kernels.cuh:7-74). */
+int ci_encode_dense_sizes(const uint8_t *d_plane, uint32_t K, uint32_t N, const uint16_t *freqs, const uint16_t *cdf,
+                          uint32_t tile_h, uint32_t tile_w, uint32_t *d_states, uint32_t *d_sizes,
+                          uint32_t *d_stream_offsets, uint64_t *stream_len, ci_stream_t stream);
+int ci_encode_dense_write(const uint8_t *d_plane, uint32_t K, uint32_t N, const uint16_t *freqs, const uint16_t *cdf,
+                          uint32_t tile_h, uint32_t tile_w, const uint32_t *d_stream_offsets, uint8_t *d_stream,
+                          uint64_t stream_len, ci_stream_t stream);
+
+/* ---- decoders ----------------------------------------------------------- */
+
+/* Exponent plane u8 [K,N].  Replaces rans_decomp_triton_tiled
+ * (comp_inference/rans_triton.py:34-168). */
+int ci_decode_plane(const ci_tiled_weight *w, uint8_t *d_out, ci_stream_t stream);
+
+/* Full weight, bf16 bits [K,N] row-major.  Replaces the three passes of
+ * rans_decompress_module_weight_bf16 (comp_inference/comp_inference.py:573-713:
+ * tiled decode, uninterleave_mantissas, reconstruct_from_exp_and_mantissa). */
+int ci_decode_bf16(const ci_tiled_weight *w, uint16_t *d_out, ci_stream_t stream);
+
+/* Dense-layout counterparts. */
+int ci_decode_plane_dense(const ci_dense_weight *w, uint8_t *d_out, ci_stream_t stream);
+int ci_decode_bf16_dense(const ci_dense_weight *w, uint16_t *d_out, ci_stream_t stream);
+
+/* ---- fused consumers ---------------------------------------------------- */
+
+/* Bytes of workspace ci_linear / ci_linear_transposed need for M activation
+ * rows and n_out output features (0 is a valid answer). */
+size_t ci_linear_workspace_bytes(uint32_t M, uint32_t n_out, uint32_t K, uint32_t tile_h);
+
+/* y[M,N] = x[M,K] . W[K,N] (+ bias[N]), W decoded on the fly and never written
+ * to global memory.  x, bias, y are bf16 bits; x rows are x_row_stride elements
+ * apart, y rows y_row_stride.  Accumulation is fp32.  Replaces
+ * fused_rans_linear_triton (comp_inference/linear_triton.py:229-552) and, for
+ * large M, the decompress + triton_matmul pair (comp_inference/triton_gemm.py:324-337).
+ * d_workspace must hold ci_linear_workspace_bytes() bytes and must have been
+ * zero-filled once when allocated; each call leaves it zeroed again.
+ * split_k = 0 lets the library choose. */
+int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M, const uint16_t *d_bias,
+              uint16_t *d_y, int64_t y_row_stride, void *d_workspace, size_t workspace_bytes, uint32_t split_k,
+              ci_stream_t stream);
+
+/* y[M,V] = x[M,H] . W[V,H]^T for a weight stored as [K=V, N=H] (LM head / tied
+ * embedding).  Replaces fused_rans_linear_transposed_triton
+ * (comp_inference/transposed_linear_triton.py:187-435). */
+int ci_linear_transposed(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M,
+                         const uint16_t *d_bias, uint16_t *d_y, int64_t y_row_stride, void *d_workspace,
+                         size_t workspace_bytes, ci_stream_t stream);
+
+/* out[i,:] = W[ids[i],:] as bf16 bits; ids outside [0,K) give a zero row.
+ * Replaces fused_rans_embedding_triton (comp_inference/embedding_triton.py:170-330). */
+int ci_embedding(const ci_tiled_weight *w, const int64_t *d_ids, uint64_t n_ids, uint16_t *d_out,
+                 int64_t out_row_stride, ci_stream_t stream);
+
+/* Dense-layout fused linear and embedding (comp_inference/linear_triton.py:1044-1265,
+ * comp_inference/embedding_triton.py:333-483). */
+int ci_linear_dense(const ci_dense_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M,
+                    const uint16_t *d_bias, uint16_t *d_y, int64_t y_row_stride, void *d_workspace,
+                    size_t workspace_bytes, uint32_t split_k, ci_stream_t stream);
+int ci_embedding_dense(const ci_dense_weight *w, const int64_t *d_ids, uint64_t n_ids, uint16_t *d_out,
+                       int64_t out_row_stride, ci_stream_t stream);
+
+/* ---- legacy flat layout -------------------------------------------------- */
+
+/* Decoder of the non-tiled legacy layout: stream g yields the symbols at flat
+ * indices g, g+num_streams, ...; its bytes sit at stride num_streams and are read
+ * from index sizes[g]-1 downwards.  Replaces ccore.decompress
+ * (src/python_bindings.cpp:61-78 -> src/cuda/rans_kernels.cuh:626-708). */
+int ci_decode_legacy(const uint8_t *d_stream, uint64_t stream_len, const uint32_t *d_states, const uint32_t *d_sizes,
+                     uint32_t num_streams, uint64_t output_len, const uint32_t *d_tables, const uint8_t *d_slot_map,
+                     uint8_t *d_out, ci_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COMP_INFERENCE_B200_H */

@@ -1,0 +1,343 @@
+"""GPU: the CUDA path, called through the C ABI (via the package's ctypes binding), against the
+CPU oracle and the committed reference fixtures.
+
+Bars: bit-exact for everything integer/byte (encoder bytes, states, offsets, decoded planes,
+bf16 weights, embedding rows); for the fused linears max |y - y_ref| / max |y_ref| <= 1e-2
+against decompress-then-matmul in fp32 (the tolerance the benchmark spec states; outputs are
+bf16, so about 4e-3 of that budget is the final rounding).
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bits, golden_case, make_weight
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def ci():
+    import comp_inference_b200 as pkg
+    from comp_inference_b200 import _lib
+    _lib.load()
+    return pkg
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.view(dtype) if t.element_size() == torch.empty(0, dtype=dtype).element_size() else t.to(dtype)
+    return t.cuda()
+
+
+def cuda_stored(g):
+    return dict(compressed_streams=dev(g["stream"]), initial_states=dev(g["states"]), tables=dev(g["tables"]),
+                slot_map=dev(g["slot_map"]), tile_offsets=dev(g["tile_offsets"]), tile_max_lens=dev(g["tile_max_lens"]))
+
+
+def rel_err(y, ref):
+    return float(np.abs(y - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+# ------------------------------------------------------------------ fixtures from the reference
+
+@pytest.mark.parametrize("i", range(6))
+def test_reference_fixture_decode_and_embedding(ci, golden, i):
+    g = golden_case(golden, i)
+    K, N, th, tw = g["K"], g["N"], g["th"], g["tw"]
+    s = cuda_stored(g)
+    plane = ci.rans_decomp_triton_tiled(**s, output_shape=(K, N), tile_k=th, tile_n=tw)
+    assert np.array_equal(plane.cpu().numpy(), g["ref_plane"])
+    w = ci.rans_decompress_bf16(s["compressed_streams"], s["initial_states"], s["tables"], s["slot_map"], (K, N),
+                                s["tile_offsets"], s["tile_max_lens"], th, tw, dev(g["man_tiled"]))
+    assert np.array_equal(bits(w), g["raw"])
+    ids = torch.from_numpy(g["emb_ids"]).cuda()
+    emb = ci.fused_rans_embedding_triton(ids, s["compressed_streams"], s["initial_states"], s["tables"], s["slot_map"],
+                                         (K, N), s["tile_offsets"], s["tile_max_lens"], th, tw, dev(g["man_tiled"]))
+    assert np.array_equal(bits(emb), g["ref_emb"])
+
+
+@pytest.mark.parametrize("i", range(6))
+def test_reference_fixture_encoder_bytes(ci, golden, i):
+    g = golden_case(golden, i)
+    r = ci.ccore.RansManager(0).compress_tiled(torch.from_numpy(g["exp"]), torch.from_numpy(g["freqs"]),
+                                               torch.from_numpy(g["cdf"]), g["th"], g["tw"])
+    assert r.success and (r.tile_height, r.tile_width) == (g["th"], g["tw"])
+    for key, mine in (("stream", r.stream), ("states", r.states), ("sizes", r.output_sizes), ("tables", r.tables),
+                      ("slot_map", r.slot_map), ("tile_offsets", r.tile_offsets), ("tile_max_lens", r.tile_max_lens)):
+        assert not mine.is_cuda
+        assert np.array_equal(mine.numpy().view(g[key].dtype), g[key]), key
+
+
+# ------------------------------------------------------------------ against the oracle, many shapes
+
+SHAPES = [
+    (96, 64, 64, 32), (100, 70, 32, 16), (256, 128, 1024, 32), (48, 33, 16, 32), (16, 8, 16, 8),
+    (130, 200, 64, 64), (64, 256, 32, 128), (1000, 96, 128, 32), (33, 5, 16, 8), (2048, 512, 1024, 32),
+    (512, 1024, 128, 32), (300, 100, 256, 16),
+]
+
+
+def compress_both(ci, oracle, K, N, th, tw, seed, std=0.02):
+    W = make_weight(K, N, seed, std)
+    o = oracle.compress_bf16(bits(W), th, tw)
+    c = ci.compress_weight_cuda(W.cuda(), th, tw)
+    return W, o, c
+
+
+@pytest.mark.parametrize("K,N,th,tw", SHAPES)
+def test_compress_matches_oracle_bit_for_bit(ci, oracle, K, N, th, tw):
+    W, o, c = compress_both(ci, oracle, K, N, th, tw, seed=K + 13 * N)
+    assert (c["tile_height"], c["tile_width"]) == (o.tile_height, o.tile_width)
+    assert np.array_equal(c["exponent_freqs"].numpy(), o["freqs"])
+    for mine, theirs in ((c["rans_exp_stream"], o.stream), (c["rans_exp_states"], o.states),
+                         (c["output_sizes"], o.output_sizes), (c["rans_exp_tables"], o.tables),
+                         (c["rans_exp_slot_map"], o.slot_map), (c["rans_exp_tile_offsets"], o.tile_offsets),
+                         (c["rans_exp_tile_max_lens"], o.tile_max_lens), (c["rans_man_raw"], o["mantissa"])):
+        assert np.array_equal(mine.cpu().numpy().view(theirs.dtype), theirs)
+
+
+@pytest.mark.parametrize("K,N,th,tw", SHAPES)
+def test_decode_matches_oracle(ci, oracle, K, N, th, tw):
+    W, o, c = compress_both(ci, oracle, K, N, th, tw, seed=2 * K + N)
+    th2, tw2 = c["tile_height"], c["tile_width"]
+    plane = ci.rans_decomp_triton_tiled(c["rans_exp_stream"], c["rans_exp_states"], c["rans_exp_tables"],
+                                        c["rans_exp_slot_map"], (K, N), c["rans_exp_tile_offsets"],
+                                        c["rans_exp_tile_max_lens"], tile_k=th2, tile_n=tw2)
+    assert np.array_equal(plane.cpu().numpy(), oracle.decode_plane(o, K, N, th2, tw2))
+    w = ci.rans_decompress_bf16(c["rans_exp_stream"], c["rans_exp_states"], c["rans_exp_tables"],
+                                c["rans_exp_slot_map"], (K, N), c["rans_exp_tile_offsets"],
+                                c["rans_exp_tile_max_lens"], th2, tw2, c["rans_man_raw"])
+    assert np.array_equal(bits(w), bits(W))
+
+
+def _linear_args(c):
+    return dict(compressed_data=c["rans_exp_stream"], initial_states=c["rans_exp_states"], tables=c["rans_exp_tables"],
+                slot_map=c["rans_exp_slot_map"], tile_offsets=c["rans_exp_tile_offsets"],
+                tile_max_lens=c["rans_exp_tile_max_lens"], tile_k=c["tile_height"], tile_n=c["tile_width"],
+                mantissas=c["rans_man_raw"])
+
+
+@pytest.mark.parametrize("K,N,th,tw", SHAPES)
+@pytest.mark.parametrize("M", [1, 3, 16])
+def test_fused_linear_matches_decompress_then_matmul(ci, oracle, K, N, th, tw, M):
+    W, o, c = compress_both(ci, oracle, K, N, th, tw, seed=5 * K + N + M)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16)
+    ref = oracle.linear(bits(x), o, o["mantissa"], K, N, c["tile_height"], c["tile_width"])
+    for split in (0, 1, 4):
+        y = ci.fused_rans_linear_triton(x.cuda(), weight_shape=(K, N), SPLIT_K=split, **_linear_args(c))
+        assert y.shape == (M, N) and y.dtype == torch.bfloat16
+        assert rel_err(y.float().cpu().numpy(), ref) <= REL_TOL, (split, rel_err(y.float().cpu().numpy(), ref))
+    # twice in a row: the split-K workspace must come back clean
+    y2 = ci.fused_rans_linear_triton(x.cuda(), weight_shape=(K, N), SPLIT_K=4, **_linear_args(c))
+    assert torch.equal(y2, y)
+
+
+def test_fused_linear_bias_out_and_leading_dims(ci, oracle):
+    K, N, th, tw = 512, 256, 64, 32
+    W, o, c = compress_both(ci, oracle, K, N, th, tw, seed=77)
+    x = torch.randn(2, 3, K, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    ref = oracle.linear(bits(x.view(-1, K)), o, o["mantissa"], K, N, th, tw) + bias.float().numpy()
+    y = ci.fused_rans_linear_triton(x.cuda(), weight_shape=(K, N), bias=bias.cuda(), **_linear_args(c))
+    assert y.shape == (2, 3, N)
+    assert rel_err(y.float().cpu().numpy().reshape(-1, N), ref) <= REL_TOL
+    out = torch.empty(6, N, dtype=torch.bfloat16, device="cuda")
+    r = ci.fused_rans_linear_triton(x.cuda(), weight_shape=(K, N), bias=bias.cuda(), out=out, **_linear_args(c))
+    assert r is out and torch.equal(out.view(2, 3, N), y)
+    # activations with a row stride (a column slice of a wider tensor) are taken as they are
+    wide = torch.randn(4, 2 * K, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).cuda()
+    ys = ci.fused_rans_linear_triton(wide[:, :K], weight_shape=(K, N), **_linear_args(c))
+    yc = ci.fused_rans_linear_triton(wide[:, :K].contiguous(), weight_shape=(K, N), **_linear_args(c))
+    assert torch.equal(ys, yc)
+
+
+@pytest.mark.parametrize("V,H,th,tw", [(96, 64, 64, 32), (1000, 256, 128, 32), (300, 96, 32, 16), (520, 128, 256, 64),
+                                        (2100, 64, 1024, 32)])
+@pytest.mark.parametrize("M", [1, 5])
+def test_transposed_linear_matches_oracle(ci, oracle, V, H, th, tw, M):
+    W, o, c = compress_both(ci, oracle, V, H, th, tw, seed=V + H)
+    x = torch.randn(M, H, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16)
+    ref = oracle.linear(bits(x), o, o["mantissa"], V, H, c["tile_height"], c["tile_width"], transposed=True)
+    y = ci.fused_rans_linear_transposed_triton(x.cuda(), weight_shape=(V, H), **_linear_args(c))
+    assert y.shape == (M, V)
+    assert rel_err(y.float().cpu().numpy(), ref) <= REL_TOL
+    assert torch.equal(ci.fused_rans_linear_transposed_triton(x.cuda(), weight_shape=(V, H), **_linear_args(c)), y)
+
+
+@pytest.mark.parametrize("K,N,th,tw", SHAPES)
+def test_embedding_rows_bit_exact(ci, oracle, K, N, th, tw):
+    W, o, c = compress_both(ci, oracle, K, N, th, tw, seed=K ^ N)
+    g = torch.Generator().manual_seed(3001)
+    ids = torch.cat([torch.randint(0, K, (50,), generator=g), torch.tensor([0, K - 1, K, -1, 2 ** 40])])
+    a = _linear_args(c)
+    emb = ci.fused_rans_embedding_triton(ids.view(5, 11).cuda(), weight_shape=(K, N), **a)
+    assert emb.shape == (5, 11, N)
+    want = oracle.embedding(ids.numpy(), o, o["mantissa"], K, N, c["tile_height"], c["tile_width"])
+    assert np.array_equal(bits(emb).reshape(-1, N), want)
+    empty = ci.fused_rans_embedding_triton(torch.empty(0, dtype=torch.int64).cuda(), weight_shape=(K, N), **a)
+    assert empty.shape == (0, N)
+
+
+@pytest.mark.parametrize("K,N,th,tw", SHAPES[:8])
+def test_dense_layout(ci, oracle, K, N, th, tw):
+    W = make_weight(K, N, seed=K + N + 1)
+    e, m = oracle.split_bf16(bits(W))
+    f, cdf = oracle.rans_lut(e)
+    o = oracle.encode_dense(e, f, cdf, th, tw)
+    c = ci.compress_weight_cuda(W.cuda(), th, tw, uncoalesced_interleaving=True)
+    th2, tw2 = c["tile_height"], c["tile_width"]
+    for mine, theirs in ((c["rans_exp_stream"], o.stream), (c["rans_exp_states"], o.states),
+                         (c["output_sizes"], o.output_sizes), (c["rans_exp_stream_offsets"], o.stream_offsets)):
+        assert np.array_equal(mine.cpu().numpy().view(theirs.dtype), theirs)
+    from comp_inference_b200 import ops
+    plane = ops.rans_decomp_uncoalesced(c["rans_exp_stream"], c["rans_exp_states"], c["rans_exp_tables"],
+                                        c["rans_exp_slot_map"], (K, N), c["rans_exp_stream_offsets"],
+                                        c["output_sizes"], th2, tw2)
+    assert np.array_equal(plane.cpu().numpy(), e)
+    x = torch.randn(3, K, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    ref = (x.double() @ W.double()).numpy()
+    y = ci.fused_rans_linear_triton_uncoalesced(x.cuda(), c["rans_exp_stream"], c["rans_exp_states"],
+                                                c["rans_exp_tables"], c["rans_exp_slot_map"], (K, N),
+                                                c["rans_exp_stream_offsets"], c["output_sizes"], th2, tw2,
+                                                c["rans_man_raw"], SPLIT_K=2)
+    assert rel_err(y.float().cpu().numpy(), ref) <= REL_TOL
+    ids = torch.tensor([0, K - 1, K // 2, K, -3])
+    emb = ci.fused_rans_embedding_triton_uncoalesced(ids.cuda(), c["rans_exp_stream"], c["rans_exp_states"],
+                                                     c["rans_exp_tables"], c["rans_exp_slot_map"], (K, N),
+                                                     c["rans_exp_stream_offsets"], c["output_sizes"], th2, tw2,
+                                                     c["rans_man_raw"])
+    for i, t in enumerate(ids.tolist()):
+        want = bits(W[t]) if 0 <= t < K else np.zeros(N, np.uint16)
+        assert np.array_equal(bits(emb[i]), want)
+
+
+def test_hard_planes_round_trip(ci, oracle):
+    """Flat, single-symbol and heavy-tailed planes (two renormalisation bytes per symbol occur)."""
+    rng = np.random.default_rng(0)
+    for plane in (rng.integers(0, 256, (64, 32), dtype=np.uint8), np.full((64, 32), 7, np.uint8),
+                  (rng.zipf(1.2, (128, 64)) % 256).astype(np.uint8)):
+        K, N = plane.shape
+        f, cdf = ci.get_rans_lut(torch.from_numpy(plane))
+        fo, co = oracle.rans_lut(plane)
+        assert np.array_equal(f.numpy(), fo) and np.array_equal(cdf.numpy(), co)
+        r = ci.ccore.RansManager().compress_tiled(torch.from_numpy(plane).cuda(), f, cdf, 32, 32)
+        o = oracle.encode_tiled(plane, fo, co, 32, 32)
+        assert np.array_equal(r.stream.numpy(), o.stream) and np.array_equal(r.states.numpy().view(np.uint32), o.states)
+        back = ci.rans_decomp_triton_tiled(r.stream.cuda(), r.states.cuda(), r.tables.cuda(), r.slot_map.cuda(), (K, N),
+                                           r.tile_offsets.cuda(), r.tile_max_lens.cuda(), tile_k=32, tile_n=32)
+        assert np.array_equal(back.cpu().numpy(), plane)
+
+
+def test_module_compress_decompress_api(ci):
+    """The reference's round-trip procedure (tests/test_reconstruction.py:58-193) on one Linear."""
+    lin = torch.nn.Linear(384, 200, bias=False, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(make_weight(200, 384, seed=21))
+    original = lin.weight.detach().clone()
+    ci.rans_compress_module_weight(lin, tile_height=128, tile_width=32)
+    assert lin.compressed == "rans_bfloat16" and not hasattr(lin, "weight")
+    assert lin.input_shape == [384, 200] and not lin.exponent_compressed_weight.is_cuda
+    ci.rans_decompress_module_weight(lin)
+    assert isinstance(lin.weight, torch.nn.Parameter)
+    assert torch.equal(lin.weight.view(torch.uint16), original.t().contiguous().view(torch.uint16))
+    e, m = ci.extract_exp_and_mantissa(original)
+    assert torch.equal(ci.reconstruct_from_exp_and_mantissa(e, m).view(torch.uint16), original.view(torch.uint16))
+    with pytest.raises(RuntimeError, match="Invalid tile height"):
+        ci.ccore.RansManager().compress_tiled(e, *ci.get_rans_lut(e), 24, 32)
+
+
+def test_runtime_modules(ci, oracle):
+    K, N = 256, 128
+    W = make_weight(K, N, seed=31)
+    c = ci.compress_weight_cuda(W.cuda(), 64, 32)
+    lin = ci.RansLinear(K, N, 64, 32).load_compressed(c)
+    x = torch.randn(4, K, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    ref = (x.double().cpu() @ W.double()).numpy()
+    assert rel_err(lin(x).float().cpu().numpy(), ref) <= REL_TOL
+    emb = ci.RansEmbedding(K, N, 64, 32).load_compressed(c)
+    ids = torch.tensor([[1, 2], [255, 0]]).cuda()
+    assert torch.equal(emb(ids).view(torch.uint16).cpu(), W[ids.cpu()].view(torch.uint16))
+    head = ci.RansLMHead(N, K, 64, 32).load_compressed(c)
+    xh = torch.randn(2, N, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).cuda()
+    refh = (xh.double().cpu() @ W.double().t()).numpy()
+    assert rel_err(head(xh).float().cpu().numpy(), refh) <= REL_TOL
+
+
+# ------------------------------------------------------------------ full benchmark sizes, by property
+
+@pytest.mark.parametrize("out_f,in_f,seed", [(4096, 4096, 1001), (11008, 4096, 1002), (4096, 11008, 1003)])
+def test_llama_shapes_round_trip_and_linearity(ci, out_f, in_f, seed):
+    """Benchmark-size weights: compress -> decode is the identity (bit-exact), and the fused linear
+    equals a dense fp32 matmul on the decoded weight within tolerance, for both tile heights used."""
+    W = make_weight(out_f, in_f, seed)                     # HF layout [out, in]
+    Wkn = W.t().contiguous().cuda()                        # stored [K=in, N=out]
+    K, N = in_f, out_f
+    for th in (1024, 128):
+        c = ci.compress_weight_cuda(Wkn, th, 32)
+        a = _linear_args(c)
+        w = ci.rans_decompress_bf16(a["compressed_data"], a["initial_states"], a["tables"], a["slot_map"], (K, N),
+                                    a["tile_offsets"], a["tile_max_lens"], th, 32, a["mantissas"])
+        assert torch.equal(w.view(torch.uint16), Wkn.view(torch.uint16))
+        for M in (1, 4, 16):
+            x = torch.randn(M, K, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).cuda()
+            y = ci.fused_rans_linear_triton(x, weight_shape=(K, N), SPLIT_K=0, **a)
+            ref = x.float() @ Wkn.float()
+            err = float((y.float() - ref).abs().max() / ref.abs().max())
+            assert err <= REL_TOL, (th, M, err)
+        stored = sum(c[k].numel() * c[k].element_size() for k in
+                     ("rans_exp_stream", "rans_exp_states", "rans_exp_tile_offsets", "rans_exp_tile_max_lens",
+                      "rans_man_raw")) + 1024 + 4096
+        assert stored < 0.75 * 2 * K * N
+
+
+def test_embedding_table_full_size(ci):
+    V, H = 32000, 4096
+    W = make_weight(V, H, 1004).cuda()
+    c = ci.compress_weight_cuda(W, 128, 32)
+    ids = torch.randint(0, V, (4096,), generator=torch.Generator().manual_seed(3001)).cuda()
+    emb = ci.fused_rans_embedding_triton(ids, weight_shape=(V, H), **_linear_args(c))
+    assert torch.equal(emb.view(torch.uint16), W[ids].view(torch.uint16))
+    x = torch.randn(2, H, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).cuda()
+    y = ci.fused_rans_linear_transposed_triton(x, weight_shape=(V, H), **_linear_args(c))
+    ref = x.float() @ W.float().t()
+    assert float((y.float() - ref).abs().max() / ref.abs().max()) <= REL_TOL
+
+
+# ------------------------------------------------------------------ the reference's own encoder, if it was built
+
+def test_reference_encoder_produces_the_same_bytes(ci):
+    """Cross-check against the reference's unmodified extension (built from its sources by
+    oracle/build.py into oracle/_ref/; skipped when that build is not present)."""
+    import importlib.util
+    import os
+    import sys
+    from conftest import ROOT
+    from oracle import build as ob
+    path = ob.ref_so_path()
+    if not os.path.exists(path):
+        pytest.skip("reference extension not built")
+    spec = importlib.util.spec_from_file_location("ccore", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    for (K, N, th, tw, seed) in [(256, 128, 64, 32, 1), (1024, 256, 1024, 32, 2), (96, 64, 32, 16, 3),
+                                 (4096, 4096, 128, 32, 1001)]:
+        W = make_weight(K, N, seed)
+        e, m = ci.extract_exp_and_mantissa(W)
+        f, cdf = ci.get_rans_lut(e)
+        mine = ci.ccore.RansManager().compress_tiled(e, f, cdf, th, tw)
+        fd = os.dup(1)
+        devnull = os.open(os.devnull, os.O_WRONLY)
+        os.dup2(devnull, 1)                                 # the reference prints on every call
+        try:
+            theirs = ref.RansManager(K * N).compress_tiled(e.contiguous(), f.contiguous(), cdf.contiguous(), th, tw)
+        finally:
+            os.dup2(fd, 1)
+            os.close(devnull)
+            os.close(fd)
+        assert theirs.success
+        for key in ("stream", "states", "output_sizes", "tables", "slot_map", "tile_offsets", "tile_max_lens"):
+            a, b = getattr(mine, key), getattr(theirs, key)
+            assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (K, N, th, tw, key)
