@@ -149,6 +149,23 @@ def prepared_lut(tables, slot_map):
     return lut
 
 
+_maxlen_cache = {}
+
+
+def max_tile_len(tile_max_lens):
+    """Largest entry of tile_max_lens (one device->host read per tensor object, then cached); the
+    staged kernels size their shared-memory byte window with it."""
+    key = tile_max_lens.data_ptr()
+    hit = _maxlen_cache.get(key)
+    if hit is not None and hit[0]() is tile_max_lens and hit[1] == tile_max_lens._version:
+        return hit[2]
+    v = int(tile_max_lens.view(torch.int32).max().item()) if tile_max_lens.numel() else 0
+    if len(_maxlen_cache) > 4096:
+        _maxlen_cache.clear()
+    _maxlen_cache[key] = (weakref.ref(tile_max_lens), tile_max_lens._version, v)
+    return v
+
+
 # ---- split-K workspace: one zero-initialised buffer per device, grown on demand
 _workspaces = {}
 
@@ -162,7 +179,7 @@ def workspace(device, nbytes):
 
 
 def tiled_weight(stream_t, states, tables, slot_map, tile_offsets, tile_max_lens, mantissa, K, N, th, tw, lut=None,
-                 keep=None):
+                 keep=None, want_max=False):
     """Fills a ci_tiled_weight from CUDA tensors; returns (struct, tensors that must stay alive)."""
     require_cuda(stream_t, "compressed stream")
     st = as_u8(stream_t, "compressed stream")
@@ -181,8 +198,9 @@ def tiled_weight(stream_t, states, tables, slot_map, tile_offsets, tile_max_lens
         raise ValueError(f"mantissa plane has {man.numel()} bytes, {tiles * th * tw} expected")
     if lut is None:
         lut = prepared_lut(tb, sm) if (tb is tables and sm is slot_map) else None
+    deepest = max_tile_len(tile_max_lens) if (want_max and ml is tile_max_lens) else 0
     w = TiledWeight(ptr(st), ptr(sts), ptr(tb), ptr(sm), ptr(off), ptr(ml), ptr(man), ptr(lut), st.numel(),
-                    K, N, th, tw, 0, 0)
+                    K, N, th, tw, deepest, 0)
     return w, (st, sts, tb, sm, off, ml, man, lut, keep)
 
 

@@ -52,7 +52,7 @@ __device__ __forceinline__ bool stage_bytes(const DecArgs &a, const LaneTask &L,
     begin = __shfl_sync(kFull, L.off, 0);
     uint32_t end = __shfl_sync(kFull, L.off + L.ml * a.g.W, 31);
     uint32_t bytes = end - begin;
-    bool ok = a.stream_aligned && a.g.tw <= 32 && bytes <= kStageBytes;
+    bool ok = a.stream_aligned && a.g.tw >= 8 && a.g.tw <= 32 && bytes <= kStageBytes;
     if (!ok) return false;
     const uint4 *src = reinterpret_cast<const uint4 *>(a.stream + begin);   // begin is a multiple of 2*tw >= 16
     uint4 *dst = reinterpret_cast<uint4 *>(win);

@@ -12,125 +12,9 @@
 // fp32 partial; the CTA that draws the last ticket of a column group sums the
 // partials in a fixed order, so results are deterministic (the reference writes
 // bf16 partials and sums them with a second kernel, linear_triton.py:302-314).
-#include "common.cuh"
+#include "linear.cuh"
 
 namespace ci {
-
-constexpr int kLinWarps = 8;
-constexpr uint32_t kLinStage = 4096;     // per-warp compressed-byte window
-constexpr uint32_t kMaxSplits = 16;
-constexpr uint32_t kTicketBytes = 4096;  // number of u32 ticket counters at the head of the workspace
-
-struct LinArgs {
-    const uint8_t *stream;
-    const uint32_t *states, *tables, *tile_offsets, *tile_max_lens, *lut;
-    const uint8_t *slot_map, *mantissa;
-    Geom g;
-    uint32_t stream_aligned;
-    const uint16_t *x;
-    int64_t ldx;
-    const uint16_t *bias;
-    uint16_t *y;
-    int64_t ldy;
-    uint32_t M;
-    uint32_t splits, tiles_per_split;
-    const uint32_t *dense_sizes, *dense_offsets;   // dense layout only
-    uint32_t *tickets;   // [items along the non-reduced dimension]
-    float *partial;      // [splits][M][n_out]
-};
-
-struct LaneTile {
-    uint32_t n, t, lc, off, ml;
-    bool live;
-};
-
-__device__ __forceinline__ LaneTile lane_tile(const LinArgs &a, uint32_t tk, uint32_t grp) {
-    LaneTile L;
-    L.n = grp * 32 + lane_id();
-    uint32_t tn = L.n / a.g.tw;
-    L.live = L.n < a.g.N;
-    if (tn >= a.g.tiles_n) tn = a.g.tiles_n - 1;
-    L.lc = L.n % a.g.tw;
-    L.t = tk * a.g.tiles_n + tn;
-    L.off = a.tile_offsets[L.t];
-    L.ml = a.tile_max_lens[L.t];
-    return L;
-}
-
-__device__ __forceinline__ bool stage_tile_bytes(const LinArgs &a, const LaneTile &L, uint8_t *win, uint32_t &begin) {
-    begin = __shfl_sync(kFull, L.off, 0);
-    uint32_t end = __shfl_sync(kFull, L.off + L.ml * a.g.W, 31);
-    uint32_t bytes = end - begin;
-    bool ok = a.stream_aligned && a.g.tw <= 32 && bytes <= kLinStage;
-    if (!ok) return false;
-    const uint4 *src = reinterpret_cast<const uint4 *>(a.stream + begin);
-    uint4 *dst = reinterpret_cast<uint4 *>(win);
-    for (uint32_t i = lane_id(); i < bytes / 16; i += 32) dst[i] = __ldg(src + i);
-    __syncwarp();
-    return true;
-}
-
-// Streams of one lane over one tile, with the byte source abstracted.
-struct TileStreams {
-    uint32_t stA, stB;
-    bool staged;
-    SmemCursor sA, sB;
-    GmemCursor gA, gB;
-    const uint8_t *win;
-    uint32_t W;
-};
-
-__device__ __forceinline__ void open_streams(const LinArgs &a, const LaneTile &L, uint8_t *win, TileStreams &S) {
-    S.stA = S.stB = kRansL;
-    if (L.live) {
-        S.stA = a.states[(size_t)L.t * a.g.W + L.lc];
-        S.stB = a.states[(size_t)L.t * a.g.W + a.g.tw + L.lc];
-    }
-    S.W = a.g.W;
-    S.win = win;
-    uint32_t begin;
-    __syncwarp();
-    S.staged = stage_tile_bytes(a, L, win, begin);
-    if (S.staged) {
-        S.sA.low = L.off - begin + L.lc;
-        S.sB.low = S.sA.low + a.g.tw;
-        uint32_t top = L.live ? (L.ml - 1) * a.g.W : 0u - a.g.W;
-        S.sA.pos = S.sA.low + top;
-        S.sB.pos = S.sB.low + top;
-    } else {
-        S.gA.base = a.stream + L.off + L.lc;
-        S.gB.base = S.gA.base + a.g.tw;
-        S.gA.row = S.gB.row = L.live ? (int32_t)L.ml - 1 : -1;
-    }
-}
-
-__device__ __forceinline__ uint32_t next_A(TileStreams &S, const uint32_t *s_lut) {
-    uint32_t e = decode_symbol(S.stA, s_lut);
-    if (S.staged) renorm_smem(S.stA, S.sA, S.win, S.W); else renorm_gmem(S.stA, S.gA, S.W);
-    return e >> 24;
-}
-__device__ __forceinline__ uint32_t next_B(TileStreams &S, const uint32_t *s_lut) {
-    uint32_t e = decode_symbol(S.stB, s_lut);
-    if (S.staged) renorm_smem(S.stB, S.sB, S.win, S.W); else renorm_gmem(S.stB, S.gB, S.W);
-    return e >> 24;
-}
-
-__device__ __forceinline__ float load_bf16(const uint16_t *p) { return __uint_as_float((uint32_t)__ldg(p) << 16); }
-
-// Draws a ticket for `slot`; returns true in the CTA that arrived last.  All
-// partial sums of this CTA must have been written before the call.
-__device__ __forceinline__ bool last_arrival(uint32_t *ticket, uint32_t expected, uint32_t *s_flag) {
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t old = atomicAdd(ticket, 1u);
-        *s_flag = (old == expected - 1u);
-    }
-    __syncthreads();
-    bool last = *s_flag != 0;
-    if (last) __threadfence();
-    return last;
-}
 
 // CTA-level tail shared by the tiled and dense kernels: sums the 8 warps' register
 // accumulators through shared memory, then stores bf16 (+bias) or goes through the
@@ -389,9 +273,14 @@ static LinArgs base_args(const ci_tiled_weight *w) {
     return a;
 }
 
+// Tickets + the larger of: split-K partials of the generic kernels, stream-K partials of the
+// staged kernel (one [M][32] fp32 slot per warp of the grid plus one per column group).
 static size_t workspace_bytes(uint32_t M, uint32_t n_out) {
     uint32_t mt = M < 16 ? M : 16;
-    return (size_t)kTicketBytes * 4 + (size_t)kMaxSplits * mt * n_out * sizeof(float);
+    size_t split = (size_t)kMaxSplits * mt * n_out * sizeof(float);
+    size_t slots = (size_t)sm_count() * 16 + (n_out + 31) / 32 + 2;
+    size_t streamk = slots * mt * 32 * sizeof(float);
+    return (size_t)kTicketBytes * 4 + (split > streamk ? split : streamk);
 }
 
 template <int MT>
@@ -466,14 +355,13 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
     if (M == 0) return CI_OK;
     CI_REQUIRE(ldx >= (int64_t)w->K && ldy >= (int64_t)w->N, "row strides smaller than the row length");
     LinArgs a = base_args(w);
-    CI_REQUIRE(a.g.groups <= kTicketBytes, "too many column groups for the ticket area");
+    CI_REQUIRE(a.g.groups < kTicketBytes, "too many column groups for the ticket area");
     choose_splits(a, split_k);
-    if (a.splits > 1) {
+    const bool have_ws = d_ws != nullptr && ws_bytes >= workspace_bytes(M, w->N);
+    if (a.splits > 1 && !have_ws) {
         CI_REQUIRE(d_ws != nullptr, "split-K needs a workspace");
-        if (ws_bytes < workspace_bytes(M, w->N)) {
-            set_error("workspace of %zu bytes, %zu needed", ws_bytes, workspace_bytes(M, w->N));
-            return CI_E_WORKSPACE;
-        }
+        set_error("workspace of %zu bytes, %zu needed", ws_bytes, workspace_bytes(M, w->N));
+        return CI_E_WORKSPACE;
     }
     a.tickets = reinterpret_cast<uint32_t *>(d_ws);
     a.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d_ws) + kTicketBytes * 4);
@@ -484,6 +372,13 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
         a.x = d_x + (size_t)m0 * ldx;
         a.y = d_y + (size_t)m0 * ldy;
         a.M = mc;
+        // staged tensor-core kernel when the weight qualifies (tile width <= 32, known maximum tile
+        // depth, aligned buffers, a workspace); split_k != 0 asks for the generic split-K kernel
+        if (split_k == 0 && have_ws) {
+            rc = launch_linear_mma(a, w->max_tile_len, s);
+            if (rc == CI_OK) continue;
+            if (rc < 0) return rc;
+        }
         if (mc == 1) rc = launch_linear<1>(a, s);
         else if (mc == 2) rc = launch_linear<2>(a, s);
         else if (mc <= 4) rc = launch_linear<4>(a, s);

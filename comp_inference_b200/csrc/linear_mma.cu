@@ -1,0 +1,400 @@
+// Fused decode + linear, staged tensor-core path (activation batches of up to 16
+// rows per pass): y[M,N] = x[M,K] . W[K,N] with W decoded from its rANS streams
+// inside the kernel.  Replaces fused_rans_matmul_kernel_ilp2_splitk
+// (comp_inference/linear_triton.py:317-552).
+//
+// Work unit: one warp decodes one (tile row, 32-column group) = 64 streams, two
+// per lane.  All bytes a unit needs -- the tile's compressed byte block and its
+// raw sign+mantissa block -- are fetched by two bulk async copies
+// (cp.async.bulk, completion on an mbarrier) into a per-warp double buffer, so the
+// copy of unit t+1 overlaps the decode of unit t and no load latency sits on the
+// decode chain.  Decoded weights are packed to bf16 in registers, transposed
+// through a 1 KB swizzled shared-memory tile and fed to mma.sync m16n8k16 with
+// the activations as the A operand; the dot products never touch CUDA-core FMAs,
+// so 16 activation rows cost the same as one.
+//
+// Scheduling: warp-level stream-K.  The units of the whole matrix, ordered by
+// column group then tile row, are cut into equal contiguous runs, one per warp of
+// a persistent one-CTA-per-SM grid.  A warp whose run ends inside a column group
+// writes an fp32 partial; the warp that draws the last ticket of the group adds
+// the partials in a fixed order (deterministic) and writes bf16.
+#include "linear.cuh"
+
+namespace ci {
+
+constexpr uint32_t kWaitPolls = 1u << 22;   // mbarrier polls before a wait gives up
+constexpr uint32_t kLutBytes = kProbScale * 4;
+constexpr uint32_t kBarBytes = 256;          // 16 warps x 2 stages x 8 B
+constexpr uint32_t kWtBytes = 2048;          // two swizzled 32x16 bf16 tiles (A-half, B-half)
+
+struct MmaArgs {
+    LinArgs a;
+    uint32_t win_cap;      // bytes reserved per stage for the compressed byte block
+    uint32_t stage_bytes;  // win_cap + mantissa block
+    uint32_t warp_bytes;   // 2 stages + transpose tiles
+    uint32_t per_warp;     // units per warp
+    uint32_t total;        // units in the matrix
+    uint32_t x_aligned;    // activations can be read as 32-bit pairs
+    uint32_t *status;      // set non-zero if a wait ran out
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// 1-D bulk copy global -> this CTA's shared memory (no multicast), 16-byte aligned, size % 16 == 0.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&x)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(b0), "r"(b1));
+}
+
+// bf16 bits of one weight from its table entry (symbol in bits 31..24) and sign+mantissa byte.
+__device__ __forceinline__ uint32_t weight_bits(uint32_t entry, uint32_t man) {
+    return ((entry >> 17) & 0x7F80u) | ((man & 0x80u) << 8) | (man & 0x7Fu);
+}
+
+// Two activations x[r][k], x[r][k+1] as one register (zero beyond M rows / K columns).
+__device__ __forceinline__ uint32_t load_x_pair(const MmaArgs &p, uint32_t r, uint32_t k) {
+    const LinArgs &a = p.a;
+    if (r >= a.M || k >= a.g.K) return 0u;
+    const uint16_t *src = a.x + (size_t)r * a.ldx + k;
+    if (p.x_aligned && k + 1 < a.g.K) return __ldg(reinterpret_cast<const uint32_t *>(src));
+    uint32_t lo = __ldg(src), hi = (k + 1 < a.g.K) ? (uint32_t)__ldg(src + 1) : 0u;
+    return lo | (hi << 16);
+}
+// A operand of mma m16n8k16 for activation columns [k0, k0+16).
+__device__ __forceinline__ void load_x_frag(const MmaArgs &p, uint32_t k0, uint32_t (&x)[4]) {
+    const uint32_t r = lane_id() >> 2, c = k0 + 2 * (lane_id() & 3);
+    x[0] = load_x_pair(p, r, c);
+    x[1] = load_x_pair(p, r + 8, c);
+    x[2] = load_x_pair(p, r, c + 8);
+    x[3] = load_x_pair(p, r + 8, c + 8);
+}
+
+// Swizzled [32 columns][16 k] bf16 tile: 32-byte rows, the two 16-byte halves of a row swapped
+// on every second group of four rows, which makes both the 16-byte row stores and the
+// ldmatrix reads bank-conflict free.
+__device__ __forceinline__ uint32_t wt_offset(uint32_t n, uint32_t khalf) {
+    return n * 32 + ((khalf ^ ((n >> 2) & 1u)) << 4);
+}
+
+__global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ MmaArgs p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const LinArgs &a = p.a;
+    const Geom &g = a.g;
+    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem);
+    const uint32_t W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = lane_id();
+    uint8_t *wbase = smem + kLutBytes + kBarBytes + (size_t)warp * p.warp_bytes;
+    uint8_t *wt = wbase + 2 * p.stage_bytes;
+    const uint32_t bar_base = smem_u32(smem + kLutBytes + warp * 16);
+
+    load_lut(s_lut, a.lut, a.tables, a.slot_map);
+    if (lane == 0) {
+        mbar_init(bar_base, 1);
+        mbar_init(bar_base + 8, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+
+    const uint32_t gw = blockIdx.x * W + warp;                  // this warp's rank in the grid
+    const uint32_t lo = gw * p.per_warp;
+    const uint32_t hi = min(lo + p.per_warp, p.total);
+    if (lo >= hi) return;                                       // no CTA-wide synchronisation below this line
+
+    const uint32_t tiles_per_group = g.tw >= 32 ? 1u : 32u / g.tw;
+    const uint32_t man_tile = g.th * g.tw;
+
+    // Queues the two bulk copies of unit t into `stage`.
+    auto issue = [&](uint32_t t, uint32_t stage) {
+        const uint32_t grp = t / g.tiles_k, tk = t - grp * g.tiles_k;
+        const uint32_t tn0 = grp * 32 / g.tw;
+        const uint32_t nt = min(tiles_per_group, g.tiles_n - tn0);
+        const uint32_t t0 = tk * g.tiles_n + tn0, tl = t0 + nt - 1;
+        if (lane == 0) {
+            const uint32_t begin = a.tile_offsets[t0];
+            uint32_t wbytes = a.tile_offsets[tl] + a.tile_max_lens[tl] * g.W - begin;
+            if (wbytes > p.win_cap) {                           // metadata disagrees with the declared maximum
+                atomicExch(p.status, 2u);
+                wbytes = 0;
+            }
+            const uint32_t mbytes = nt * man_tile;
+            const uint32_t bar = bar_base + stage * 8;
+            const uint32_t dst = smem_u32(wbase + (size_t)stage * p.stage_bytes);
+            fence_async_proxy();
+            mbar_expect_tx(bar, wbytes + mbytes);
+            if (wbytes) bulk_load(dst, a.stream + begin, wbytes, bar);
+            bulk_load(dst + p.win_cap, a.mantissa + (size_t)t0 * man_tile, mbytes, bar);
+        }
+    };
+
+    float acc[4][4];
+    auto zero_acc = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    };
+
+    // Writes the finished (or partial) sums of column group grp.
+    auto flush = [&](uint32_t grp) {
+        const uint32_t first_w = (grp * g.tiles_k) / p.per_warp;
+        const uint32_t last_w = ((grp + 1) * g.tiles_k - 1) / p.per_warp;
+        const uint32_t count = last_w - first_w + 1;
+        const uint32_t r0 = lane >> 2, c0 = 2 * (lane & 3);
+        auto store_y = [&](uint32_t m, uint32_t n, float v0, float v1) {
+            if (m >= a.M) return;
+            if (n < g.N) {
+                if (a.bias) v0 += load_bf16(a.bias + n);
+                a.y[(size_t)m * a.ldy + n] = float_to_bf16_bits(v0);
+            }
+            if (n + 1 < g.N) {
+                if (a.bias) v1 += load_bf16(a.bias + n + 1);
+                a.y[(size_t)m * a.ldy + n + 1] = float_to_bf16_bits(v1);
+            }
+        };
+        if (count == 1) {
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+                store_y(r0, grp * 32 + nb * 8 + c0, acc[nb][0], acc[nb][1]);
+                store_y(r0 + 8, grp * 32 + nb * 8 + c0, acc[nb][2], acc[nb][3]);
+            }
+            return;
+        }
+        // Slot gw + grp is unique: along the unit order both the warp rank and the group only grow.
+        float *mine = a.partial + (size_t)(gw + grp) * a.M * 32;
+#pragma unroll
+        for (int nb = 0; nb < 4; ++nb) {
+            if (r0 < a.M) *reinterpret_cast<float2 *>(mine + r0 * 32 + nb * 8 + c0) = make_float2(acc[nb][0], acc[nb][1]);
+            if (r0 + 8 < a.M)
+                *reinterpret_cast<float2 *>(mine + (r0 + 8) * 32 + nb * 8 + c0) = make_float2(acc[nb][2], acc[nb][3]);
+        }
+        __threadfence();
+        __syncwarp();
+        uint32_t last = 0;
+        if (lane == 0) last = atomicAdd(a.tickets + grp, 1u) == count - 1;
+        last = __shfl_sync(kFull, last, 0);
+        if (!last) return;
+        __threadfence();
+#pragma unroll
+        for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t m = r0 + 8 * h;
+                if (m >= a.M) continue;
+                float v0 = 0.f, v1 = 0.f;
+                for (uint32_t w = first_w; w <= last_w; ++w) {
+                    float2 v = __ldcg(reinterpret_cast<const float2 *>(a.partial + (size_t)(w + grp) * a.M * 32 + m * 32 +
+                                                                         nb * 8 + c0));
+                    v0 += v.x;
+                    v1 += v.y;
+                }
+                store_y(m, grp * 32 + nb * 8 + c0, v0, v1);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) a.tickets[grp] = 0;                      // ready for the next call
+    };
+
+    uint32_t parity0 = 0, parity1 = 0, stage = 0;
+    uint32_t cur_grp = lo / g.tiles_k;
+    zero_acc();
+    issue(lo, 0);
+
+    for (uint32_t t = lo; t < hi; ++t) {
+        const uint32_t grp = t / g.tiles_k, tk = t - grp * g.tiles_k;
+        if (grp != cur_grp) {
+            flush(cur_grp);
+            zero_acc();
+            cur_grp = grp;
+        }
+        if (t + 1 < hi) issue(t + 1, stage ^ 1);
+
+        // ---- this lane's two streams ---------------------------------------
+        LaneTile L = lane_tile(a, tk, grp);
+        const uint32_t begin = __shfl_sync(kFull, L.off, 0);
+        const uint32_t t0 = __shfl_sync(kFull, L.t, 0);
+        uint32_t stA = kRansL, stB = kRansL;
+        if (L.live) {
+            stA = a.states[(size_t)L.t * g.W + L.lc];
+            stB = a.states[(size_t)L.t * g.W + g.tw + L.lc];
+        }
+        const uint8_t *win = wbase + (size_t)stage * p.stage_bytes;
+        const uint8_t *man = win + p.win_cap + (L.t - t0) * man_tile + L.lc;
+        SmemCursor cA, cB;
+        cA.low = L.off - begin + L.lc;
+        cB.low = cA.low + g.tw;
+        {
+            const uint32_t top = L.live ? (L.ml - 1) * g.W : 0u - g.W;
+            cA.pos = cA.low + top;
+            cB.pos = cB.low + top;
+        }
+        const uint32_t row0 = tk * g.th, remain = g.K - row0;
+        const uint32_t nA = min(remain, g.half), nB = remain > g.half ? min(remain - g.half, g.half) : 0;
+
+        // ---- wait for the bytes (bounded) -------------------------------------
+        {
+            const uint32_t bar = bar_base + stage * 8, par = stage ? parity1 : parity0;
+            uint32_t ok = 0;
+            if (lane == 0)
+                for (uint32_t it = 0; it < kWaitPolls && !ok; ++it) ok = mbar_try_wait(bar, par);
+            ok = __shfl_sync(kFull, ok, 0);
+            if (stage) parity1 ^= 1; else parity0 ^= 1;
+            if (!ok) {
+                if (lane == 0) atomicExch(p.status, 1u);
+                stage ^= 1;
+                continue;
+            }
+        }
+
+        // ---- decode 16 rows of each half at a time, multiply on the tensor cores
+        for (uint32_t i0 = 0; i0 < nA; i0 += 16) {
+            uint32_t xa[4], xb[4];
+            load_x_frag(p, row0 + i0, xa);
+            load_x_frag(p, row0 + g.half + i0, xb);
+            uint32_t pa[8], pb[8];
+            if (i0 + 16 <= nB) {                                // full block of both halves
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t i = i0 + 2 * j;
+                    uint32_t e0 = decode_symbol(stA, s_lut);
+                    renorm_smem(stA, cA, win, g.W);
+                    uint32_t f0 = decode_symbol(stB, s_lut);
+                    renorm_smem(stB, cB, win, g.W);
+                    uint32_t e1 = decode_symbol(stA, s_lut);
+                    renorm_smem(stA, cA, win, g.W);
+                    uint32_t f1 = decode_symbol(stB, s_lut);
+                    renorm_smem(stB, cB, win, g.W);
+                    pa[j] = weight_bits(e0, man[i * g.tw]) | (weight_bits(e1, man[(i + 1) * g.tw]) << 16);
+                    pb[j] = weight_bits(f0, man[(g.half + i) * g.tw]) | (weight_bits(f1, man[(g.half + i + 1) * g.tw]) << 16);
+                }
+            } else {                                            // ragged end: rows beyond the matrix contribute zero
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    uint32_t h[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const uint32_t i = i0 + 2 * j + q;
+                        if (i < nA) {
+                            uint32_t e = decode_symbol(stA, s_lut);
+                            renorm_smem(stA, cA, win, g.W);
+                            h[q] = weight_bits(e, man[i * g.tw]);
+                        }
+                        if (i < nB) {
+                            uint32_t e = decode_symbol(stB, s_lut);
+                            renorm_smem(stB, cB, win, g.W);
+                            h[2 + q] = weight_bits(e, man[(g.half + i) * g.tw]);
+                        }
+                    }
+                    pa[j] = h[0] | (h[1] << 16);
+                    pb[j] = h[2] | (h[3] << 16);
+                }
+            }
+            __syncwarp();                                       // previous block's ldmatrix reads are done
+            *reinterpret_cast<uint4 *>(wt + wt_offset(lane, 0)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+            *reinterpret_cast<uint4 *>(wt + wt_offset(lane, 1)) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
+            *reinterpret_cast<uint4 *>(wt + 1024 + wt_offset(lane, 0)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
+            *reinterpret_cast<uint4 *>(wt + 1024 + wt_offset(lane, 1)) = make_uint4(pb[4], pb[5], pb[6], pb[7]);
+            __syncwarp();
+            const uint32_t mat = lane >> 3, r = lane & 7;
+            const uint32_t wt_s = smem_u32(wt);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const uint32_t n = (2 * c + (mat >> 1)) * 8 + r;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(wt_s + wt_offset(n, mat & 1), b0, b1, b2, b3);
+                mma_bf16(acc[2 * c], xa, b0, b1);
+                mma_bf16(acc[2 * c + 1], xa, b2, b3);
+                if (i0 < nB) {
+                    ldmatrix_x4(wt_s + 1024 + wt_offset(n, mat & 1), b0, b1, b2, b3);
+                    mma_bf16(acc[2 * c], xb, b0, b1);
+                    mma_bf16(acc[2 * c + 1], xb, b2, b3);
+                }
+            }
+        }
+        stage ^= 1;
+    }
+    flush(cur_grp);
+}
+
+// ------------------------------------------------------------------------ host
+
+int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
+    const Geom &g = a.g;
+    if (!(g.tw == 8 || g.tw == 16 || g.tw == 32)) return 1;
+    if ((reinterpret_cast<uintptr_t>(a.stream) & 15u) || (reinterpret_cast<uintptr_t>(a.mantissa) & 15u)) return 1;
+    if (max_tile_len == 0) return 1;                            // unknown: cannot size the byte window
+    if (a.M > 16 || (g.th * g.tw) % 16 != 0) return 1;
+
+    int dev = 0, max_smem = 0;
+    CI_CUDA(cudaGetDevice(&dev));
+    CI_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    MmaArgs p;
+    p.a = a;
+    p.win_cap = ((max_tile_len * 64u + 15u) & ~15u) + 16u;
+    p.stage_bytes = p.win_cap + g.th * 32u;
+    p.warp_bytes = 2 * p.stage_bytes + kWtBytes;
+    p.warp_bytes = (p.warp_bytes + 127u) & ~127u;
+    const uint32_t fixed = kLutBytes + kBarBytes;
+    if ((uint32_t)max_smem < fixed + 4 * p.warp_bytes) return 1;
+    uint32_t w_max = ((uint32_t)max_smem - fixed) / p.warp_bytes;
+    if (w_max > 16) w_max = 16;
+
+    // Units per warp must be a whole number: pick the warp count whose grid wastes the least.
+    const uint32_t P = (uint32_t)sm_count();
+    p.total = g.groups * g.tiles_k;
+    uint32_t best_w = w_max;
+    double best = -1.0;
+    for (uint32_t w = 4; w <= w_max; ++w) {
+        uint64_t slots = (uint64_t)P * w, per = (p.total + slots - 1) / slots;
+        double eff = (double)p.total / (double)(slots * per);
+        if (w < 8) eff *= w / 8.0;                              // too few warps cannot hide the decode chain
+        if (eff >= best) { best = eff; best_w = w; }
+    }
+    const uint64_t slots = (uint64_t)P * best_w;
+    p.per_warp = (uint32_t)((p.total + slots - 1) / slots);
+    const uint32_t warps_needed = (p.total + p.per_warp - 1) / p.per_warp;
+    const uint32_t blocks = (warps_needed + best_w - 1) / best_w;
+    p.x_aligned = ((reinterpret_cast<uintptr_t>(a.x) & 3u) == 0 && (a.ldx & 1) == 0) ? 1u : 0u;
+    p.status = a.tickets + (kTicketBytes - 1);
+
+    const size_t smem = fixed + (size_t)best_w * p.warp_bytes;
+    static size_t attr = 0;
+    if (smem > attr) {
+        CI_CUDA(cudaFuncSetAttribute(k_linear_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+        attr = (size_t)max_smem;
+    }
+    k_linear_mma<<<blocks, best_w * 32, smem, s>>>(p);
+    CI_LAUNCH_CHECK(k_linear_mma);
+    return CI_OK;
+}
+
+}  // namespace ci

@@ -36,7 +36,7 @@ int check_tile(uint32_t K, uint32_t N, uint32_t th, uint32_t tw) {
     CI_REQUIRE(K > 0 && N > 0, "empty matrix %u x %u", K, N);
     // src/cuda/rans_host.cuh:440-445: the tile height must be a multiple of 16
     CI_REQUIRE(th >= 16 && th % 16 == 0, "tile height %u is not a positive multiple of 16", th);
-    CI_REQUIRE(tw == 8 || tw == 16 || tw == 32 || tw == 64 || tw == 128, "tile width %u not in {8,16,32,64,128}", tw);
+    CI_REQUIRE(tw >= 1 && tw <= 128 && (tw & (tw - 1)) == 0, "tile width %u is not a power of two in [1,128]", tw);
     return CI_OK;
 }
 

@@ -90,7 +90,7 @@ def fused_rans_linear_triton(x, compressed_data, initial_states, tables, slot_ma
     x2 = _check_x(x, K)
     M = x2.shape[0]
     w, keep = _lib.tiled_weight(compressed_data, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
-                                mantissas, K, N, int(tile_k), int(tile_n))
+                                mantissas, K, N, int(tile_k), int(tile_n), want_max=True)
     y = _linear_call(w, x2, M, N, bias, out, SPLIT_K, False)
     return out if out is not None else y.view(*x.shape[:-1], N)
 

@@ -62,7 +62,7 @@ typedef struct ci_tiled_weight {
     const uint32_t *lut;           /* optional: [4096] from ci_prepare_lut, or NULL (kernels then build it themselves) */
     uint64_t stream_len;           /* bytes in stream                                   */
     uint32_t K, N;                 /* logical matrix                                    */
-    uint32_t tile_h, tile_w;       /* tile_h % 16 == 0; tile_w in {8,16,32,64,128}      */
+    uint32_t tile_h, tile_w;       /* tile_h % 16 == 0; tile_w a power of two <= 128   */
     uint32_t max_tile_len;         /* max over tile_max_lens if known, else 0           */
     uint32_t reserved;
 } ci_tiled_weight;
