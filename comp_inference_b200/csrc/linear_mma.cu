@@ -81,6 +81,58 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&x)[4], 
 __device__ __forceinline__ uint32_t weight_bits(uint32_t entry, uint32_t man) {
     return ((entry >> 17) & 0x7F80u) | ((man & 0x80u) << 8) | (man & 0x7Fu);
 }
+// Two weights (rows k, k+1 of one column) as a packed bf16 pair, five instructions:
+// both symbols are brought to bits 14..7 / 30..23 with one byte permute, both
+// sign+mantissa bytes are doubled into their halves with another, one bit-select merges.
+__device__ __forceinline__ uint32_t weight_pair(uint32_t e_lo, uint32_t e_hi, uint32_t m_lo, uint32_t m_hi) {
+    const uint32_t ee = __byte_perm(e_lo >> 17, e_hi >> 1, 0x7610);
+    const uint32_t vv = __byte_perm(m_lo, m_hi, 0x4400);
+    return (ee & 0x7F807F80u) | (vv & 0x807F807Fu);
+}
+
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// One symbol with the table at shared address lut_s.
+__device__ __forceinline__ uint32_t decode_fast(uint32_t &state, uint32_t lut_s) {
+    const uint32_t e = lds_u32(lut_s + ((state & kProbMask) << 2));
+    state = ((e >> 12) & 0xFFFu) * (state >> kProbBits) + (e & 0xFFFu);
+    return e;
+}
+// First renormalisation byte, STRIDE bytes between the rows of a stream.  No lower-bound test:
+// a well-formed stream always has a byte left when its state is below 2^16, and the launcher
+// guarantees enough mapped shared memory below every window that a malformed stream reads
+// garbage instead of faulting.
+template <uint32_t STRIDE>
+__device__ __forceinline__ void renorm_fast(uint32_t &state, uint32_t &pos) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .u32 b;\n\t"
+        "setp.lt.u32 p, %0, 65536;\n\t"
+        "@p ld.shared.u8 b, [%1];\n\t"
+        "@p mad.lo.u32 %0, %0, 256, b;\n\t"
+        "@p sub.u32 %1, %1, %2;\n\t}"
+        : "+r"(state), "+r"(pos)
+        : "n"(STRIDE));
+}
+// Both streams of a lane after one symbol each; the rare second byte is probed only when some
+// lane of the warp still needs it.
+template <uint32_t STRIDE>
+__device__ __forceinline__ void renorm_pair(uint32_t &sa, uint32_t &pa, uint32_t &sb, uint32_t &pb) {
+    renorm_fast<STRIDE>(sa, pa);
+    renorm_fast<STRIDE>(sb, pb);
+    if (__any_sync(kFull, (sa < kRansL) | (sb < kRansL))) {
+        renorm_fast<STRIDE>(sa, pa);
+        renorm_fast<STRIDE>(sb, pb);
+    }
+}
 
 // Two activations x[r][k], x[r][k+1] as one register (zero beyond M rows / K columns).
 __device__ __forceinline__ uint32_t load_x_pair(const MmaArgs &p, uint32_t r, uint32_t k) {
@@ -91,13 +143,21 @@ __device__ __forceinline__ uint32_t load_x_pair(const MmaArgs &p, uint32_t r, ui
     uint32_t lo = __ldg(src), hi = (k + 1 < a.g.K) ? (uint32_t)__ldg(src + 1) : 0u;
     return lo | (hi << 16);
 }
-// A operand of mma m16n8k16 for activation columns [k0, k0+16).
+// A operand of mma m16n8k16 for activation columns [k0, k0+16), any position (guards on M and K).
 __device__ __forceinline__ void load_x_frag(const MmaArgs &p, uint32_t k0, uint32_t (&x)[4]) {
     const uint32_t r = lane_id() >> 2, c = k0 + 2 * (lane_id() & 3);
     x[0] = load_x_pair(p, r, c);
     x[1] = load_x_pair(p, r + 8, c);
     x[2] = load_x_pair(p, r, c + 8);
     x[3] = load_x_pair(p, r + 8, c + 8);
+}
+// Same for a block known to lie inside the matrix and 4-byte aligned activations:
+// x0 / x1 point at this lane's element of rows r and r+8 (null when the row does not exist).
+__device__ __forceinline__ void load_x_frag_fast(const uint16_t *x0, const uint16_t *x1, uint32_t k0, uint32_t (&x)[4]) {
+    x[0] = x0 ? __ldg(reinterpret_cast<const uint32_t *>(x0 + k0)) : 0u;
+    x[1] = x1 ? __ldg(reinterpret_cast<const uint32_t *>(x1 + k0)) : 0u;
+    x[2] = x0 ? __ldg(reinterpret_cast<const uint32_t *>(x0 + k0 + 8)) : 0u;
+    x[3] = x1 ? __ldg(reinterpret_cast<const uint32_t *>(x1 + k0 + 8)) : 0u;
 }
 
 // Swizzled [32 columns][16 k] bf16 tile: 32-byte rows, the two 16-byte halves of a row swapped
@@ -106,55 +166,62 @@ __device__ __forceinline__ void load_x_frag(const MmaArgs &p, uint32_t k0, uint3
 __device__ __forceinline__ uint32_t wt_offset(uint32_t n, uint32_t khalf) {
     return n * 32 + ((khalf ^ ((n >> 2) & 1u)) << 4);
 }
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
+template <uint32_t TW>
 __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ MmaArgs p) {
+    constexpr uint32_t WB = 2 * TW;                             // bytes per row of a tile's byte block
+    constexpr uint32_t TPG = 32 / TW;                           // tiles per 32-column group
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs &a = p.a;
     const Geom &g = a.g;
     uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem);
     const uint32_t W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = lane_id();
-    uint8_t *wbase = smem + kLutBytes + kBarBytes + (size_t)warp * p.warp_bytes;
-    uint8_t *wt = wbase + 2 * p.stage_bytes;
-    const uint32_t bar_base = smem_u32(smem + kLutBytes + warp * 16);
-
-    load_lut(s_lut, a.lut, a.tables, a.slot_map);
-    if (lane == 0) {
-        mbar_init(bar_base, 1);
-        mbar_init(bar_base + 8, 1);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncthreads();
+    const uint32_t smem_s = smem_u32(smem);
+    const uint32_t wbase_s = smem_s + kLutBytes + kBarBytes + warp * p.warp_bytes;
+    const uint32_t wt_s = wbase_s + 2 * p.stage_bytes;
+    const uint32_t bar_base = smem_s + kLutBytes + warp * 16;
+    const uint32_t man_tile = g.th * TW;
 
     const uint32_t gw = blockIdx.x * W + warp;                  // this warp's rank in the grid
     const uint32_t lo = gw * p.per_warp;
     const uint32_t hi = min(lo + p.per_warp, p.total);
-    if (lo >= hi) return;                                       // no CTA-wide synchronisation below this line
-
-    const uint32_t tiles_per_group = g.tw >= 32 ? 1u : 32u / g.tw;
-    const uint32_t man_tile = g.th * g.tw;
 
     // Queues the two bulk copies of unit t into `stage`.
     auto issue = [&](uint32_t t, uint32_t stage) {
+        if (lane != 0) return;
         const uint32_t grp = t / g.tiles_k, tk = t - grp * g.tiles_k;
-        const uint32_t tn0 = grp * 32 / g.tw;
-        const uint32_t nt = min(tiles_per_group, g.tiles_n - tn0);
+        const uint32_t tn0 = grp * TPG;
+        const uint32_t nt = min(TPG, g.tiles_n - tn0);
         const uint32_t t0 = tk * g.tiles_n + tn0, tl = t0 + nt - 1;
-        if (lane == 0) {
-            const uint32_t begin = a.tile_offsets[t0];
-            uint32_t wbytes = a.tile_offsets[tl] + a.tile_max_lens[tl] * g.W - begin;
-            if (wbytes > p.win_cap) {                           // metadata disagrees with the declared maximum
-                atomicExch(p.status, 2u);
-                wbytes = 0;
-            }
-            const uint32_t mbytes = nt * man_tile;
-            const uint32_t bar = bar_base + stage * 8;
-            const uint32_t dst = smem_u32(wbase + (size_t)stage * p.stage_bytes);
-            fence_async_proxy();
-            mbar_expect_tx(bar, wbytes + mbytes);
-            if (wbytes) bulk_load(dst, a.stream + begin, wbytes, bar);
-            bulk_load(dst + p.win_cap, a.mantissa + (size_t)t0 * man_tile, mbytes, bar);
+        const uint32_t begin = a.tile_offsets[t0];
+        uint32_t wbytes = a.tile_offsets[tl] + a.tile_max_lens[tl] * WB - begin;
+        if (wbytes > p.win_cap) {                               // metadata disagrees with the declared maximum
+            atomicExch(p.status, 2u);
+            wbytes = 0;
         }
+        const uint32_t mbytes = nt * man_tile;
+        const uint32_t bar = bar_base + stage * 8;
+        const uint32_t dst = wbase_s + stage * p.stage_bytes;
+        fence_async_proxy();
+        mbar_expect_tx(bar, wbytes + mbytes);
+        if (wbytes) bulk_load(dst, a.stream + begin, wbytes, bar);
+        bulk_load(dst + p.win_cap, a.mantissa + (size_t)t0 * man_tile, mbytes, bar);
     };
+
+    // The first copy is started before the table is loaded so both latencies overlap.
+    if (lane == 0) {
+        mbar_init(bar_base, 1);
+        mbar_init(bar_base + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (lo < hi) issue(lo, 0);
+    load_lut(s_lut, a.lut, a.tables, a.slot_map);
+    __syncthreads();
+    if (lo >= hi) return;                                       // no CTA-wide synchronisation below this line
 
     float acc[4][4];
     auto zero_acc = [&]() {
@@ -224,10 +291,18 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
         if (lane == 0) a.tickets[grp] = 0;                      // ready for the next call
     };
 
+    // this lane's activation rows (fragment rows r and r+8), offset to its column pair
+    const uint32_t xr = lane >> 2, xc = 2 * (lane & 3);
+    const uint16_t *x0 = xr < a.M ? a.x + (size_t)xr * a.ldx + xc : nullptr;
+    const uint16_t *x1 = xr + 8 < a.M ? a.x + (size_t)(xr + 8) * a.ldx + xc : nullptr;
+    const uint32_t mat = lane >> 3, mr = lane & 7;
+    const uint32_t ld_off0 = wt_offset((mat >> 1) * 8 + mr, mat & 1);          // n-blocks 0,1
+    const uint32_t ld_off1 = wt_offset((2 + (mat >> 1)) * 8 + mr, mat & 1);    // n-blocks 2,3
+    const uint32_t st_off0 = wt_offset(lane, 0), st_off1 = wt_offset(lane, 1);
+
     uint32_t parity0 = 0, parity1 = 0, stage = 0;
     uint32_t cur_grp = lo / g.tiles_k;
     zero_acc();
-    issue(lo, 0);
 
     for (uint32_t t = lo; t < hi; ++t) {
         const uint32_t grp = t / g.tiles_k, tk = t - grp * g.tiles_k;
@@ -244,21 +319,17 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
         const uint32_t t0 = __shfl_sync(kFull, L.t, 0);
         uint32_t stA = kRansL, stB = kRansL;
         if (L.live) {
-            stA = a.states[(size_t)L.t * g.W + L.lc];
-            stB = a.states[(size_t)L.t * g.W + g.tw + L.lc];
+            stA = a.states[(size_t)L.t * WB + L.lc];
+            stB = a.states[(size_t)L.t * WB + TW + L.lc];
         }
-        const uint8_t *win = wbase + (size_t)stage * p.stage_bytes;
-        const uint8_t *man = win + p.win_cap + (L.t - t0) * man_tile + L.lc;
-        SmemCursor cA, cB;
-        cA.low = L.off - begin + L.lc;
-        cB.low = cA.low + g.tw;
-        {
-            const uint32_t top = L.live ? (L.ml - 1) * g.W : 0u - g.W;
-            cA.pos = cA.low + top;
-            cB.pos = cB.low + top;
-        }
+        const uint32_t win_s = wbase_s + stage * p.stage_bytes;
+        uint32_t man_s = win_s + p.win_cap + (L.t - t0) * man_tile + L.lc;      // (row 0, this column)
+        uint32_t posA = win_s + (L.off - begin) + L.lc, posB;
+        if (L.live) posA += (L.ml - 1) * WB;                    // last byte row; an empty tile starts one row below
+        posB = posA + TW;
         const uint32_t row0 = tk * g.th, remain = g.K - row0;
         const uint32_t nA = min(remain, g.half), nB = remain > g.half ? min(remain - g.half, g.half) : 0;
+        const uint32_t manB_off = g.half * TW;
 
         // ---- wait for the bytes (bounded) -------------------------------------
         {
@@ -276,68 +347,77 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
         }
 
         // ---- decode 16 rows of each half at a time, multiply on the tensor cores
+        const uint32_t lut_s = smem_s;
         for (uint32_t i0 = 0; i0 < nA; i0 += 16) {
             uint32_t xa[4], xb[4];
-            load_x_frag(p, row0 + i0, xa);
-            load_x_frag(p, row0 + g.half + i0, xb);
-            uint32_t pa[8], pb[8];
-            if (i0 + 16 <= nB) {                                // full block of both halves
+            uint32_t pa[4], pb[4];                              // four packed row pairs at a time
+            const bool full = i0 + 16 <= nB;
+            if (full && p.x_aligned) {
+                load_x_frag_fast(x0, x1, row0 + i0, xa);
+                load_x_frag_fast(x0, x1, row0 + g.half + i0, xb);
+            } else {
+                load_x_frag(p, row0 + i0, xa);
+                load_x_frag(p, row0 + g.half + i0, xb);
+            }
+            __syncwarp();                                       // the previous block's ldmatrix reads are done
+            if (full) {                                         // 16 rows of both halves, no bounds tests
+#pragma unroll 1
+                for (uint32_t hb = 0; hb < 2; ++hb) {           // eight rows per pass keeps register use bounded
+                    const uint32_t mA = man_s + (i0 + 8 * hb) * TW, mB = mA + manB_off;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint32_t i = i0 + 2 * j;
-                    uint32_t e0 = decode_symbol(stA, s_lut);
-                    renorm_smem(stA, cA, win, g.W);
-                    uint32_t f0 = decode_symbol(stB, s_lut);
-                    renorm_smem(stB, cB, win, g.W);
-                    uint32_t e1 = decode_symbol(stA, s_lut);
-                    renorm_smem(stA, cA, win, g.W);
-                    uint32_t f1 = decode_symbol(stB, s_lut);
-                    renorm_smem(stB, cB, win, g.W);
-                    pa[j] = weight_bits(e0, man[i * g.tw]) | (weight_bits(e1, man[(i + 1) * g.tw]) << 16);
-                    pb[j] = weight_bits(f0, man[(g.half + i) * g.tw]) | (weight_bits(f1, man[(g.half + i + 1) * g.tw]) << 16);
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t ma0 = lds_u8(mA + (2 * j) * TW), ma1 = lds_u8(mA + (2 * j + 1) * TW);
+                        const uint32_t mb0 = lds_u8(mB + (2 * j) * TW), mb1 = lds_u8(mB + (2 * j + 1) * TW);
+                        const uint32_t e0 = decode_fast(stA, lut_s);
+                        const uint32_t f0 = decode_fast(stB, lut_s);
+                        renorm_pair<WB>(stA, posA, stB, posB);
+                        const uint32_t e1 = decode_fast(stA, lut_s);
+                        const uint32_t f1 = decode_fast(stB, lut_s);
+                        renorm_pair<WB>(stA, posA, stB, posB);
+                        pa[j] = weight_pair(e0, e1, ma0, ma1);
+                        pb[j] = weight_pair(f0, f1, mb0, mb1);
+                    }
+                    const uint32_t so = hb ? st_off1 : st_off0;
+                    sts_v4(wt_s + so, pa[0], pa[1], pa[2], pa[3]);
+                    sts_v4(wt_s + 1024 + so, pb[0], pb[1], pb[2], pb[3]);
                 }
             } else {                                            // ragged end: rows beyond the matrix contribute zero
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    uint32_t h[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        const uint32_t i = i0 + 2 * j + q;
-                        if (i < nA) {
-                            uint32_t e = decode_symbol(stA, s_lut);
-                            renorm_smem(stA, cA, win, g.W);
-                            h[q] = weight_bits(e, man[i * g.tw]);
-                        }
-                        if (i < nB) {
-                            uint32_t e = decode_symbol(stB, s_lut);
-                            renorm_smem(stB, cB, win, g.W);
-                            h[2 + q] = weight_bits(e, man[(g.half + i) * g.tw]);
-                        }
+#pragma unroll 1
+                for (uint32_t r = 0; r < 16; ++r) {
+                    const uint32_t i = i0 + r;
+                    uint32_t hA = 0, hB = 0;
+                    if (i < nA) {
+                        const uint32_t e = decode_fast(stA, lut_s);
+                        renorm_fast<WB>(stA, posA);
+                        if (__any_sync(kFull, stA < kRansL)) renorm_fast<WB>(stA, posA);
+                        hA = weight_bits(e, lds_u8(man_s + i * TW));
                     }
-                    pa[j] = h[0] | (h[1] << 16);
-                    pb[j] = h[2] | (h[3] << 16);
+                    if (i < nB) {
+                        const uint32_t e = decode_fast(stB, lut_s);
+                        renorm_fast<WB>(stB, posB);
+                        if (__any_sync(kFull, stB < kRansL)) renorm_fast<WB>(stB, posB);
+                        hB = weight_bits(e, lds_u8(man_s + manB_off + i * TW));
+                    }
+                    const uint32_t o = wt_s + ((r & 8) ? st_off1 : st_off0) + (r & 7) * 2;
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(o), "h"((uint16_t)hA) : "memory");
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(o + 1024), "h"((uint16_t)hB) : "memory");
                 }
             }
-            __syncwarp();                                       // previous block's ldmatrix reads are done
-            *reinterpret_cast<uint4 *>(wt + wt_offset(lane, 0)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
-            *reinterpret_cast<uint4 *>(wt + wt_offset(lane, 1)) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
-            *reinterpret_cast<uint4 *>(wt + 1024 + wt_offset(lane, 0)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
-            *reinterpret_cast<uint4 *>(wt + 1024 + wt_offset(lane, 1)) = make_uint4(pb[4], pb[5], pb[6], pb[7]);
             __syncwarp();
-            const uint32_t mat = lane >> 3, r = lane & 7;
-            const uint32_t wt_s = smem_u32(wt);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const uint32_t n = (2 * c + (mat >> 1)) * 8 + r;
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(wt_s + wt_offset(n, mat & 1), b0, b1, b2, b3);
-                mma_bf16(acc[2 * c], xa, b0, b1);
-                mma_bf16(acc[2 * c + 1], xa, b2, b3);
-                if (i0 < nB) {
-                    ldmatrix_x4(wt_s + 1024 + wt_offset(n, mat & 1), b0, b1, b2, b3);
-                    mma_bf16(acc[2 * c], xb, b0, b1);
-                    mma_bf16(acc[2 * c + 1], xb, b2, b3);
-                }
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(wt_s + ld_off0, b0, b1, b2, b3);
+            mma_bf16(acc[0], xa, b0, b1);
+            mma_bf16(acc[1], xa, b2, b3);
+            ldmatrix_x4(wt_s + ld_off1, b0, b1, b2, b3);
+            mma_bf16(acc[2], xa, b0, b1);
+            mma_bf16(acc[3], xa, b2, b3);
+            if (i0 < nB) {
+                ldmatrix_x4(wt_s + 1024 + ld_off0, b0, b1, b2, b3);
+                mma_bf16(acc[0], xb, b0, b1);
+                mma_bf16(acc[1], xb, b2, b3);
+                ldmatrix_x4(wt_s + 1024 + ld_off1, b0, b1, b2, b3);
+                mma_bf16(acc[2], xb, b0, b1);
+                mma_bf16(acc[3], xb, b2, b3);
             }
         }
         stage ^= 1;
@@ -347,12 +427,27 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
 
 // ------------------------------------------------------------------------ host
 
+template <uint32_t TW>
+static int launch_tw(const MmaArgs &p, uint32_t blocks, uint32_t warps, size_t smem, int max_smem, cudaStream_t s) {
+    static bool attr = false;
+    if (!attr) {
+        CI_CUDA(cudaFuncSetAttribute(k_linear_mma<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+        attr = true;
+    }
+    k_linear_mma<TW><<<blocks, warps * 32, smem, s>>>(p);
+    CI_LAUNCH_CHECK(k_linear_mma);
+    return CI_OK;
+}
+
 int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     const Geom &g = a.g;
     if (!(g.tw == 8 || g.tw == 16 || g.tw == 32)) return 1;
     if ((reinterpret_cast<uintptr_t>(a.stream) & 15u) || (reinterpret_cast<uintptr_t>(a.mantissa) & 15u)) return 1;
     if (max_tile_len == 0) return 1;                            // unknown: cannot size the byte window
     if (a.M > 16 || (g.th * g.tw) % 16 != 0) return 1;
+    // The kernel does not bounds-test stream cursors; a malformed stream can walk at most
+    // tile_h rows below its window, which must still be inside the CTA's shared memory.
+    if (g.th * g.W > kLutBytes) return 1;
 
     int dev = 0, max_smem = 0;
     CI_CUDA(cudaGetDevice(&dev));
@@ -387,14 +482,9 @@ int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     p.status = a.tickets + (kTicketBytes - 1);
 
     const size_t smem = fixed + (size_t)best_w * p.warp_bytes;
-    static size_t attr = 0;
-    if (smem > attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_linear_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr = (size_t)max_smem;
-    }
-    k_linear_mma<<<blocks, best_w * 32, smem, s>>>(p);
-    CI_LAUNCH_CHECK(k_linear_mma);
-    return CI_OK;
+    if (g.tw == 32) return launch_tw<32>(p, blocks, best_w, smem, max_smem, s);
+    if (g.tw == 16) return launch_tw<16>(p, blocks, best_w, smem, max_smem, s);
+    return launch_tw<8>(p, blocks, best_w, smem, max_smem, s);
 }
 
 }  // namespace ci
