@@ -64,13 +64,14 @@ int check_weight(const ci_tiled_weight *w, bool need_mantissa);
 #ifdef __CUDACC__
 
 // ---- decode table -----------------------------------------------------------
-// entry[slot] = bias | freq << 12 | sym << 24 with bias = slot - cdf[sym].
+// entry[slot] = bias | sym << 12 | freq << 20 with bias = slot - cdf[sym]: the two operands of the
+// state update come out with one instruction each (freq = e >> 20, bias = e & 0xFFF).
 // A frequency of 4096 (single-symbol alphabet) wraps to 0 in its 12-bit field;
 // the state then stops being meaningful but every slot still maps to that one
 // symbol and such a plane has no stream bytes, so decoding stays exact.
 __device__ __forceinline__ uint32_t make_lut_entry(uint32_t slot, uint32_t sym, uint32_t packed) {
     uint32_t freq = packed & 0xFFFFu, cdf = packed >> 16;
-    return ((slot - cdf) & 0xFFFu) | ((freq & 0xFFFu) << 12) | (sym << 24);
+    return ((slot - cdf) & 0xFFFu) | (sym << 12) | ((freq & 0xFFFu) << 20);
 }
 
 // Fills a 4096-entry shared-memory table, either by copying a prepared one or by
@@ -89,11 +90,13 @@ __device__ __forceinline__ void load_lut(uint32_t *s_lut, const uint32_t *lut, c
     }
 }
 
+__device__ __forceinline__ uint32_t lut_sym(uint32_t e) { return (e >> 12) & 0xFFu; }
+
 // One symbol: comp_inference/rans_triton.py:92-105 with the two lookups merged.
-// Returns the table entry; the symbol is entry >> 24.
+// Returns the table entry; the symbol is lut_sym(entry).
 __device__ __forceinline__ uint32_t decode_symbol(uint32_t &state, const uint32_t *s_lut) {
     uint32_t e = s_lut[state & kProbMask];
-    state = ((e >> 12) & 0xFFFu) * (state >> kProbBits) + (e & 0xFFFu);
+    state = (e >> 20) * (state >> kProbBits) + (e & 0xFFFu);
     return e;
 }
 

@@ -65,7 +65,7 @@ template <bool BF16>
 __device__ __forceinline__ void emit(const DecArgs &a, const LaneTask &L, void *out, uint32_t row, uint32_t lr,
                                      uint32_t entry) {
     size_t o = (size_t)row * a.g.N + L.n;
-    uint32_t sym = entry >> 24;
+    uint32_t sym = lut_sym(entry);
     if (BF16) {
         uint32_t m = __ldg(a.mantissa + (size_t)L.t * a.g.th * a.g.tw + (size_t)lr * a.g.tw + L.lc);
         reinterpret_cast<uint16_t *>(out)[o] = (uint16_t)assemble_bf16(sym, m);
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(256) k_decode_dense(DenseArgs a, void *out) {
         renorm_gmem(state, c, 1);
         if (live) {
             size_t o = (size_t)(row0 + i) * a.g.N + slot;
-            uint32_t sym = e >> 24;
+            uint32_t sym = lut_sym(e);
             if (BF16) {
                 uint32_t m = __ldg(a.mantissa + t * a.g.th * a.g.tw + (size_t)i * a.g.tw + lc);
                 reinterpret_cast<uint16_t *>(out)[o] = (uint16_t)assemble_bf16(sym, m);
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(256) k_decode_legacy(const uint8_t *__restrict
         uint32_t e = decode_symbol(state, s_lut);
         renorm_gmem(state, c, num_streams);
         uint64_t o = (uint64_t)gid + i * num_streams;
-        if (live && o < output_len) out[o] = (uint8_t)(e >> 24);
+        if (live && o < output_len) out[o] = (uint8_t)lut_sym(e);
     }
 }
 

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(kEmbWarps * 32) k_embedding(EmbArgs a) {
             decode_symbol(state, s_lut);
             renorm_gmem(state, c, a.g.W);
         }
-        uint32_t sym = s_lut[state & kProbMask] >> 24;
+        uint32_t sym = lut_sym(s_lut[state & kProbMask]);
         if (live) {
             uint32_t m = __ldg(a.mantissa + t * a.g.th * a.g.tw + (size_t)rel * a.g.tw + lc);
             *dst = (uint16_t)assemble_bf16(sym, m);
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kEmbWarps * 32) k_embedding_dense(EmbDenseArgs
             decode_symbol(state, s_lut);
             renorm_gmem(state, c, 1);
         }
-        uint32_t sym = s_lut[state & kProbMask] >> 24;
+        uint32_t sym = lut_sym(s_lut[state & kProbMask]);
         if (live) {
             uint32_t m = __ldg(a.mantissa + t * a.g.th * a.g.tw + (size_t)rel * a.g.tw + lc);
             *dst = (uint16_t)assemble_bf16(sym, m);

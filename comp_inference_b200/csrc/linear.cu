@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(kLinWarps * 32) k_linear_dense(LinArgs a) {
             for (uint32_t i = 0; i < rows; ++i) {
                 uint32_t e = decode_symbol(state, s_lut);
                 renorm_gmem(state, c, 1);
-                float wv = bf16_bits_to_float(assemble_bf16(e >> 24, __ldg(man + (size_t)i * a.g.tw)));
+                float wv = bf16_bits_to_float(assemble_bf16(lut_sym(e), __ldg(man + (size_t)i * a.g.tw)));
 #pragma unroll
                 for (int m = 0; m < MT; ++m)
                     if (m < (int)a.M) acc[m] = fmaf(load_bf16(a.x + (size_t)m * a.ldx + row0 + i), wv, acc[m]);

@@ -95,12 +95,12 @@ __device__ __forceinline__ void open_streams(const LinArgs &a, const LaneTile &L
 __device__ __forceinline__ uint32_t next_A(TileStreams &S, const uint32_t *s_lut) {
     uint32_t e = decode_symbol(S.stA, s_lut);
     if (S.staged) renorm_smem(S.stA, S.sA, S.win, S.W); else renorm_gmem(S.stA, S.gA, S.W);
-    return e >> 24;
+    return lut_sym(e);
 }
 __device__ __forceinline__ uint32_t next_B(TileStreams &S, const uint32_t *s_lut) {
     uint32_t e = decode_symbol(S.stB, s_lut);
     if (S.staged) renorm_smem(S.stB, S.sB, S.win, S.W); else renorm_gmem(S.stB, S.gB, S.W);
-    return e >> 24;
+    return lut_sym(e);
 }
 
 __device__ __forceinline__ float load_bf16(const uint16_t *p) { return __uint_as_float((uint32_t)__ldg(p) << 16); }

@@ -77,15 +77,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&x)[4], 
         : "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(b0), "r"(b1));
 }
 
-// bf16 bits of one weight from its table entry (symbol in bits 31..24) and sign+mantissa byte.
+// bf16 bits of one weight from its table entry (symbol in bits 19..12) and sign+mantissa byte.
 __device__ __forceinline__ uint32_t weight_bits(uint32_t entry, uint32_t man) {
-    return ((entry >> 17) & 0x7F80u) | ((man & 0x80u) << 8) | (man & 0x7Fu);
+    return ((entry >> 5) & 0x7F80u) | ((man & 0x80u) << 8) | (man & 0x7Fu);
 }
 // Two weights (rows k, k+1 of one column) as a packed bf16 pair, five instructions:
 // both symbols are brought to bits 14..7 / 30..23 with one byte permute, both
 // sign+mantissa bytes are doubled into their halves with another, one bit-select merges.
 __device__ __forceinline__ uint32_t weight_pair(uint32_t e_lo, uint32_t e_hi, uint32_t m_lo, uint32_t m_hi) {
-    const uint32_t ee = __byte_perm(e_lo >> 17, e_hi >> 1, 0x7610);
+    const uint32_t ee = __byte_perm(e_lo >> 5, e_hi << 11, 0x7610);
     const uint32_t vv = __byte_perm(m_lo, m_hi, 0x4400);
     return (ee & 0x7F807F80u) | (vv & 0x807F807Fu);
 }
@@ -104,13 +104,29 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
 // One symbol with the table at shared address lut_s.
 __device__ __forceinline__ uint32_t decode_fast(uint32_t &state, uint32_t lut_s) {
     const uint32_t e = lds_u32(lut_s + ((state & kProbMask) << 2));
-    state = ((e >> 12) & 0xFFFu) * (state >> kProbBits) + (e & 0xFFFu);
+    state = (e >> 20) * (state >> kProbBits) + (e & 0xFFFu);
     return e;
 }
-// First renormalisation byte, STRIDE bytes between the rows of a stream.  No lower-bound test:
-// a well-formed stream always has a byte left when its state is below 2^16, and the launcher
-// guarantees enough mapped shared memory below every window that a malformed stream reads
-// garbage instead of faulting.
+// Renormalisation, STRIDE bytes between the rows of a stream.  The first byte is loaded before the
+// state update is known to need it (its address does not depend on the new state, and some lane of
+// the warp needs it on nearly every step anyway), which takes one shared-memory latency off the
+// decode chain; the improbable second byte stays predicated.  No lower-bound test: a well-formed
+// stream always has a byte left when its state is below 2^16, and the launcher guarantees enough
+// mapped shared memory below every window that a malformed stream reads garbage instead of faulting.
+template <uint32_t STRIDE>
+__device__ __forceinline__ void renorm_spec(uint32_t &state, uint32_t &pos, uint32_t first) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .u32 b;\n\t"
+        "setp.lt.u32 p, %0, 65536;\n\t"
+        "@p mad.lo.u32 %0, %0, 256, %2;\n\t"
+        "@p sub.u32 %1, %1, %3;\n\t"
+        "setp.lt.u32 p, %0, 65536;\n\t"
+        "@p ld.shared.u8 b, [%1];\n\t"
+        "@p mad.lo.u32 %0, %0, 256, b;\n\t"
+        "@p sub.u32 %1, %1, %3;\n\t}"
+        : "+r"(state), "+r"(pos)
+        : "r"(first), "n"(STRIDE));
+}
 template <uint32_t STRIDE>
 __device__ __forceinline__ void renorm_fast(uint32_t &state, uint32_t &pos) {
     asm volatile(
@@ -121,17 +137,6 @@ __device__ __forceinline__ void renorm_fast(uint32_t &state, uint32_t &pos) {
         "@p sub.u32 %1, %1, %2;\n\t}"
         : "+r"(state), "+r"(pos)
         : "n"(STRIDE));
-}
-// Both streams of a lane after one symbol each; the rare second byte is probed only when some
-// lane of the warp still needs it.
-template <uint32_t STRIDE>
-__device__ __forceinline__ void renorm_pair(uint32_t &sa, uint32_t &pa, uint32_t &sb, uint32_t &pb) {
-    renorm_fast<STRIDE>(sa, pa);
-    renorm_fast<STRIDE>(sb, pb);
-    if (__any_sync(kFull, (sa < kRansL) | (sb < kRansL))) {
-        renorm_fast<STRIDE>(sa, pa);
-        renorm_fast<STRIDE>(sb, pb);
-    }
 }
 
 // Two activations x[r][k], x[r][k+1] as one register (zero beyond M rows / K columns).
@@ -368,12 +373,17 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
                     for (int j = 0; j < 4; ++j) {
                         const uint32_t ma0 = lds_u8(mA + (2 * j) * TW), ma1 = lds_u8(mA + (2 * j + 1) * TW);
                         const uint32_t mb0 = lds_u8(mB + (2 * j) * TW), mb1 = lds_u8(mB + (2 * j + 1) * TW);
+                        uint32_t ba = lds_u8(posA), bb = lds_u8(posB);
                         const uint32_t e0 = decode_fast(stA, lut_s);
                         const uint32_t f0 = decode_fast(stB, lut_s);
-                        renorm_pair<WB>(stA, posA, stB, posB);
+                        renorm_spec<WB>(stA, posA, ba);
+                        renorm_spec<WB>(stB, posB, bb);
+                        ba = lds_u8(posA);
+                        bb = lds_u8(posB);
                         const uint32_t e1 = decode_fast(stA, lut_s);
                         const uint32_t f1 = decode_fast(stB, lut_s);
-                        renorm_pair<WB>(stA, posA, stB, posB);
+                        renorm_spec<WB>(stA, posA, ba);
+                        renorm_spec<WB>(stB, posB, bb);
                         pa[j] = weight_pair(e0, e1, ma0, ma1);
                         pb[j] = weight_pair(f0, f1, mb0, mb1);
                     }

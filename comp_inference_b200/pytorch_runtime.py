@@ -10,7 +10,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .ops import (fused_rans_embedding_triton, fused_rans_linear_transposed_triton, fused_rans_linear_triton)
+from . import ops
 
 _BUFFERS = (("rans_exp_stream", torch.uint8), ("rans_exp_states", torch.uint32), ("rans_exp_tables", torch.uint32),
             ("rans_exp_slot_map", torch.uint8), ("rans_exp_tile_offsets", torch.uint32),
@@ -43,11 +43,20 @@ class _RansBase(nn.Module):
                 setattr(self, name, c[name])
         return self
 
-    def _args(self):
-        return dict(compressed_data=self.rans_exp_stream, initial_states=self.rans_exp_states,
-                    tables=self.rans_exp_tables, slot_map=self.rans_exp_slot_map,
-                    tile_offsets=self.rans_exp_tile_offsets, tile_max_lens=self.rans_exp_tile_max_lens,
-                    tile_k=self.tile_k, tile_n=self.tile_n, mantissas=self.rans_man_raw)
+    _handle = None
+
+    def _weight(self, K, N):
+        """The ci_tiled_weight descriptor of this module's buffers, built once (with the prepared decode
+        table and the deepest tile) and rebuilt only if a buffer was replaced."""
+        key = (self.rans_exp_stream.data_ptr(), self.rans_exp_states.data_ptr(), self.rans_man_raw.data_ptr(),
+               self.rans_exp_tile_offsets.data_ptr(), self.tile_k, self.tile_n)
+        if self._handle is None or self._handle[0] != key:
+            w, keep = _lib.tiled_weight(self.rans_exp_stream, self.rans_exp_states, self.rans_exp_tables,
+                                        self.rans_exp_slot_map, self.rans_exp_tile_offsets,
+                                        self.rans_exp_tile_max_lens, self.rans_man_raw, K, N, int(self.tile_k),
+                                        int(self.tile_n), want_max=True)
+            self._handle = (key, w, keep)
+        return self._handle[1]
 
 
 class RansLinear(_RansBase):
@@ -65,8 +74,11 @@ class RansLinear(_RansBase):
             self.bias = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return fused_rans_linear_triton(x=x, weight_shape=(self.in_features, self.out_features), bias=self.bias,
-                                        SPLIT_K=self.split_k if self.split_k > 1 else 0, **self._args())
+        K, N = self.in_features, self.out_features
+        x2 = ops._check_x(x, K)
+        y = ops._linear_call(self._weight(K, N), x2, x2.shape[0], N, self.bias, None,
+                             self.split_k if self.split_k > 1 else 0, False)
+        return y.view(*x.shape[:-1], N)
 
 
 class RansLMHead(_RansBase):
@@ -79,8 +91,10 @@ class RansLMHead(_RansBase):
         self._register()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return fused_rans_linear_transposed_triton(x=x, weight_shape=(self.out_features, self.in_features),
-                                                   bias=None, SPLIT_K=1, **self._args())
+        V, H = self.out_features, self.in_features
+        x2 = ops._check_x(x, H)
+        y = ops._linear_call(self._weight(V, H), x2, x2.shape[0], V, None, None, 0, True)
+        return y.view(*x.shape[:-1], V)
 
 
 class RansEmbedding(_RansBase):
@@ -93,8 +107,12 @@ class RansEmbedding(_RansBase):
         self._register()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return fused_rans_embedding_triton(x=x, weight_shape=(self.num_embeddings, self.embedding_dim),
-                                           **self._args())
+        V, H = self.num_embeddings, self.embedding_dim
+        ids = _lib.require_cuda(x, "x").reshape(-1).to(torch.int64).contiguous()
+        out = torch.empty((ids.numel(), H), device=x.device, dtype=torch.bfloat16)
+        _lib.check(_lib.load().ci_embedding(self._weight(V, H), _lib.ptr(ids), ids.numel(), _lib.ptr(out), H,
+                                            _lib.stream()))
+        return out.view(*x.shape, H)
 
 
 def patch_model(model, state_dict, layer_configs=None, default_th=1024, default_tw=32, split_k=1):

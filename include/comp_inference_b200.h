@@ -97,7 +97,7 @@ int ci_device_info(int *sm_count, int *max_smem_per_block);
 int ci_build_tables(const uint16_t *freqs, const uint16_t *cdf, uint32_t *tables, uint8_t *slot_map);
 
 /* Device.  Merges tables + slot_map into the 4096-entry decode table the
- * kernels keep in shared memory: entry[slot] = bias | freq << 12 | sym << 24,
+ * kernels keep in shared memory: entry[slot] = bias | sym << 12 | freq << 20,
  * bias = slot - cdf[sym].  (The reference's decoders do two dependent global
  * lookups per symbol instead: comp_inference/rans_triton.py:95-105.) */
 int ci_prepare_lut(const uint32_t *d_tables, const uint8_t *d_slot_map, uint32_t *d_lut, ci_stream_t stream);
