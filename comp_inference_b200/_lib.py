@@ -64,6 +64,8 @@ SIGNATURES = {
     "ci_linear_workspace_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "ci_linear": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V, C.c_size_t,
                             C.c_uint32, _S]),
+    "ci_linear_static_max_bytes": (C.c_size_t, []),
+    "ci_linear_static": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _S]),
     "ci_linear_transposed": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V,
                                        C.c_size_t, _S]),
     "ci_embedding": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_uint64, _V, C.c_int64, _S]),

@@ -478,3 +478,69 @@ int ci_linear_dense(const ci_dense_weight *w, const uint16_t *d_x, int64_t ldx, 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Fused linear for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc (or any allocating routine) on the path that
+// runs the model: a serving process whose device memory was carved up front between tenants and
+// whose allocator is then closed, a plug-in sandbox that only receives input and output buffers, a
+// runtime that must not touch the allocator once it is streaming tokens.  ci_linear needs
+// scratch memory (the stream-K / split-K ticket counters and fp32 partial sums) that such a caller
+// has no way to provide.  This variant keeps that scratch inside the library, in the fixed array
+// below, so the caller passes nothing but the weight, the activations and the output.
+//
+// The price: the array has a fixed size (kStaticScratchBytes, 16 MiB), every GPU whose context loads
+// this library holds it until the process exits, and all calls on a device share it.
+static __device__ __align__(256) unsigned char ci_static_scratch[16u << 20];
+
+namespace ci {
+constexpr size_t kStaticScratchBytes = 16u << 20;
+constexpr uint32_t kStaticMaxRows = 16;
+// In host code the array's name is only a stand-in; the device address is asked for once per device,
+// with that device current, and remembered.
+static void *g_static_scratch_ptr[64] = {nullptr};
+
+static int static_scratch(void **out) {
+    int dev = 0;
+    CI_CUDA(cudaGetDevice(&dev));
+    CI_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void *p = nullptr;
+        CI_CUDA(cudaGetSymbolAddress(&p, ci_static_scratch));
+        CI_REQUIRE(p != nullptr, "no device address for the built-in scratch array");
+        g_static_scratch_ptr[dev] = p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return CI_OK;
+}
+}  // namespace ci
+
+extern "C" {
+
+size_t ci_linear_static_max_bytes(void) { return ci::kStaticScratchBytes; }
+
+int ci_linear_static(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M, const uint16_t *d_bias,
+                     uint16_t *d_y, int64_t ldy, ci_stream_t stream) {
+    CI_REQUIRE(w != nullptr, "null weight descriptor");
+    if (M > ci::kStaticMaxRows) {
+        ci::set_error("ci_linear_static takes at most %u activation rows per call, got %u", ci::kStaticMaxRows, M);
+        return CI_E_WORKSPACE;
+    }
+    const size_t need = ci_linear_workspace_bytes(M, w->N, w->K, w->tile_h);
+    if (need > ci::kStaticScratchBytes) {
+        ci::set_error("ci_linear_static: %u x %u outputs need %zu bytes of scratch, the built-in array holds %zu; "
+                      "use ci_linear with a caller-provided workspace", M, w->N, need, ci::kStaticScratchBytes);
+        return CI_E_WORKSPACE;
+    }
+    void *scratch = nullptr;
+    int rc = ci::static_scratch(&scratch);          // first call on a device: looks the address up
+    if (rc) return rc;
+    // The array keeps whatever the last call left.  Only the ticket counters have to start at zero (a
+    // call that ended normally leaves them so; this also covers one that did not); partial sums are
+    // always written before they are read.
+    CI_CUDA(cudaMemsetAsync(scratch, 0, (size_t)ci::kTicketBytes * 4, (cudaStream_t)stream));
+    return ci_linear(w, d_x, ldx, M, d_bias, d_y, ldy, scratch, ci::kStaticScratchBytes, 0, stream);
+}
+
+}  // extern "C"

@@ -190,6 +190,24 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_strid
               uint16_t *d_y, int64_t y_row_stride, void *d_workspace, size_t workspace_bytes, uint32_t split_k,
               ci_stream_t stream);
 
+/* ci_linear for callers that cannot allocate device memory (no counterpart in the reference).
+ *
+ * Meant for hosts that are forbidden to call cudaMalloc or any allocating routine while the model
+ * runs -- a server whose device memory was handed out in advance and whose allocator is closed, a
+ * plug-in that is only given input and output buffers.  The ticket counters and fp32 partial sums
+ * that ci_linear takes as d_workspace live in a fixed 16 MiB array inside the library instead
+ * (ci_linear_static_max_bytes()); every GPU that loads the library holds that array until exit.
+ * The call itself allocates nothing and frees nothing.
+ *
+ * Limits: M <= 16 activation rows, and ci_linear_workspace_bytes(M, N, K, tile_h) must fit in the
+ * array (true for N up to about 16000 at M = 16); otherwise CI_E_WORKSPACE with the sizes in
+ * ci_last_error().  The first call on a device looks up the array's device address (with that
+ * device current); make that first call outside any stream capture.  All calls on a device share
+ * the array: two calls that overlap on the GPU (different streams, no ordering) race on it. */
+size_t ci_linear_static_max_bytes(void);
+int ci_linear_static(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M,
+                     const uint16_t *d_bias, uint16_t *d_y, int64_t y_row_stride, ci_stream_t stream);
+
 /* y[M,V] = x[M,H] . W[V,H]^T for a weight stored as [K=V, N=H] (LM head / tied
  * embedding).  Replaces fused_rans_linear_transposed_triton
  * (comp_inference/transposed_linear_triton.py:187-435). */
