@@ -50,6 +50,16 @@ NCU_TRAFFIC_4096 = 24.16e6
 NCU_BYTES_4096 = 24.06e6
 
 
+def trace(msg):
+    """Progress lines on stderr when CI_BENCH_TRACE is set (to locate a stall in a multi-rank run)."""
+    if os.environ.get("CI_BENCH_TRACE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - _T0:.1f}s] {msg}", file=sys.stderr,
+              flush=True)
+
+
+_T0 = time.perf_counter()
+
+
 def make_weight_kn(K, N, seed):
     """HF weight [out, in] = randn * 0.02 in bf16 from a CPU generator, returned as stored: [K=in, N=out]."""
     g = torch.Generator().manual_seed(seed)
@@ -201,10 +211,13 @@ def run_ours(args):
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU path for --impl ours")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    trace("start")
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+        trace("process group up")
     M = args.batch
     mods, wbytes, notes = build_block(rank, world, device)
+    trace("weights compressed and sharded")
 
     gen = torch.Generator().manual_seed(2000 + M)
     x_host = torch.randn(M, HIDDEN, generator=gen).to(torch.bfloat16).pin_memory()
@@ -215,6 +228,7 @@ def run_ours(args):
     for _ in range(3):
         y = block_step(mods, x_dev, world)
     torch.cuda.synchronize()
+    trace("eager warm-up done")
     side = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
@@ -223,6 +237,7 @@ def run_ours(args):
         with torch.cuda.graph(graph, stream=side):
             y_graph = block_step(mods, x_dev, world)
     torch.cuda.synchronize()
+    trace("graph captured")
 
     def barrier():
         if world > 1:
@@ -243,6 +258,7 @@ def run_ours(args):
     e1.record()
     barrier()
     dev_ms = e0.elapsed_time(e1) / args.steps
+    trace(f"device loop done {dev_ms:.3f} ms/step")
 
     # ---- end to end: public module API, host buffers, copies inside the timed region ------
     for _ in range(max(args.warmup, 3)):
@@ -258,6 +274,7 @@ def run_ours(args):
     e3.record()
     barrier()
     e2e_ms = e2.elapsed_time(e3) / args.steps
+    trace("e2e loop done")
     clocks = sampler.stop() if sampler else None
 
     if world > 1:
@@ -304,7 +321,16 @@ def run_ours(args):
                                               "CPU restatement of the reference algorithm, all host cores"}
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # The captured graph still refers to the NCCL communicator; tearing the process group down while
+        # it exists blocked for minutes on the 2-GPU box.  Drop the graph, line the ranks up, and leave
+        # communicator clean-up to process exit.
+        trace("shutting down")
+        del graph, y_graph
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
