@@ -180,6 +180,13 @@ def workspace(device, nbytes):
     return ws
 
 
+def kernel_status(device):
+    """Status word the staged kernels set when a bounded wait ran out or metadata was inconsistent
+    (0 = fine).  Reading it synchronises with the device."""
+    ws = _workspaces.get(torch.device(device))
+    return 0 if ws is None else int(ws[4095 * 4:4096 * 4].view(torch.int32).item())
+
+
 def tiled_weight(stream_t, states, tables, slot_map, tile_offsets, tile_max_lens, mantissa, K, N, th, tw, lut=None,
                  keep=None, want_max=False):
     """Fills a ci_tiled_weight from CUDA tensors; returns (struct, tensors that must stay alive)."""

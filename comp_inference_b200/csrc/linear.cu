@@ -343,8 +343,9 @@ using namespace ci;
 extern "C" {
 
 size_t ci_linear_workspace_bytes(uint32_t M, uint32_t n_out, uint32_t K, uint32_t tile_h) {
-    (void)K; (void)tile_h;
-    return workspace_bytes(M, n_out);
+    size_t small = workspace_bytes(M, n_out);
+    size_t big = (size_t)kTicketBytes * 4 + gemm_workspace_bytes(M, n_out, K, tile_h);    // prefill path, split-K partials
+    return small > big ? small : big;
 }
 
 int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M, const uint16_t *d_bias,
@@ -367,7 +368,14 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
     a.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d_ws) + kTicketBytes * 4);
     a.bias = d_bias; a.ldx = ldx; a.ldy = ldy;
     cudaStream_t s = (cudaStream_t)stream;
-    for (uint32_t m0 = 0; m0 < M; m0 += 16) {                   // larger batches: 16 activation rows per pass
+    if (M > 16 && d_ws != nullptr && ws_bytes > (size_t)kTicketBytes * 4) {
+        // prefill: tcgen05 decode-GEMM over all rows at once (split_k: 0 = library's choice)
+        a.x = d_x; a.y = d_y; a.M = M;
+        rc = launch_linear_gemm(a, w->max_tile_len, ws_bytes - (size_t)kTicketBytes * 4, split_k, s);
+        if (rc == CI_OK) return CI_OK;
+        if (rc < 0) return rc;
+    }
+    for (uint32_t m0 = 0; m0 < M; m0 += 16) {                   // otherwise: 16 activation rows per pass
         uint32_t mc = M - m0 < 16 ? M - m0 : 16;
         a.x = d_x + (size_t)m0 * ldx;
         a.y = d_y + (size_t)m0 * ldy;

@@ -125,4 +125,10 @@ __device__ __forceinline__ bool last_arrival(uint32_t *ticket, uint32_t expected
 // weight does not qualify (the caller then uses the generic kernel), < 0 on error.
 int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s);
 
+// tcgen05 decode-GEMM for many activation rows (gemm_sm100.cu); same return convention.
+// partial_capacity = bytes available behind a.partial for split-K partial sums.
+int launch_linear_gemm(const LinArgs &a, uint32_t max_tile_len, size_t partial_capacity, uint32_t split_k,
+                       cudaStream_t s);
+size_t gemm_workspace_bytes(uint32_t M, uint32_t N, uint32_t K, uint32_t th);
+
 }  // namespace ci

@@ -23,7 +23,6 @@
 
 namespace ci {
 
-constexpr uint32_t kLutBytes = kProbScale * 4;
 constexpr uint32_t kBarBytes = 256;          // 16 warps x 2 stages x 8 B
 constexpr uint32_t kWtBytes = 2048;          // two swizzled 32x16 bf16 tiles (A-half, B-half)
 
@@ -69,9 +68,6 @@ __device__ __forceinline__ void load_x_frag_fast(const uint16_t *x0, const uint1
 // ldmatrix reads bank-conflict free.
 __device__ __forceinline__ uint32_t wt_offset(uint32_t n, uint32_t khalf) {
     return n * 32 + ((khalf ^ ((n >> 2) & 1u)) << 4);
-}
-__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 template <uint32_t TW>

@@ -6,6 +6,7 @@
 namespace ci {
 
 constexpr uint32_t kWaitPolls = 1u << 22;   // mbarrier polls before a wait gives up
+constexpr uint32_t kLutBytes = kProbScale * 4;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -108,6 +109,10 @@ __device__ __forceinline__ void renorm_fast(uint32_t &state, uint32_t &pos) {
         : "n"(STRIDE));
 }
 
+
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
 // Lane 0 polls an mbarrier phase, bounded; the verdict is broadcast to the warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity) {

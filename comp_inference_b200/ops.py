@@ -65,7 +65,7 @@ def _linear_call(w, x2, M, n_out, bias, out, split_k, transposed):
     y = out.view(M, n_out) if out is not None else torch.empty((M, n_out), device=dev, dtype=torch.bfloat16)
     if y.dtype != torch.bfloat16 or y.stride(1) != 1:
         raise RuntimeError("out must be a bfloat16 tensor with unit inner stride")
-    nbytes = lib.ci_linear_workspace_bytes(M, n_out, 0, 0)
+    nbytes = lib.ci_linear_workspace_bytes(M, n_out, 0 if transposed else w.K, 0 if transposed else w.tile_h)
     ws = _lib.workspace(dev, nbytes)
     b = _bias(bias, n_out)
     if transposed:

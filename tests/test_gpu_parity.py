@@ -341,3 +341,38 @@ def test_reference_encoder_produces_the_same_bytes(ci):
         for key in ("stream", "states", "output_sizes", "tables", "slot_map", "tile_offsets", "tile_max_lens"):
             a, b = getattr(mine, key), getattr(theirs, key)
             assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), (K, N, th, tw, key)
+
+
+# ------------------------------------------------------------------ prefill: tcgen05 decode-GEMM
+
+@pytest.mark.parametrize("K,N,M", [(256, 128, 40), (200, 160, 300), (1024, 512, 512), (512, 256, 1000)])
+@pytest.mark.parametrize("split", [0, 1, 2])
+def test_prefill_gemm_small_shapes(ci, K, N, M, split):
+    """Many activation rows: ragged K (last tile row partial), N not a multiple of 128, M not a multiple of 256."""
+    from comp_inference_b200 import _lib
+    W = make_weight(K, N, seed=K + N).cuda()
+    c = ci.compress_weight_cuda(W, 128, 32)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16).cuda()
+    y = ci.fused_rans_linear_triton(x, weight_shape=(K, N), SPLIT_K=split, **_linear_args(c))
+    ref = x.float() @ W.float()
+    err = float((y.float() - ref).abs().max() / ref.abs().max())
+    assert err <= REL_TOL, err
+    assert _lib.kernel_status(x.device) == 0
+    y2 = ci.fused_rans_linear_triton(x, weight_shape=(K, N), SPLIT_K=split, **_linear_args(c))
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("out_f,in_f,seed", [(4096, 4096, 1001), (11008, 4096, 1002), (4096, 11008, 1003)])
+def test_prefill_gemm_llama_shapes(ci, out_f, in_f, seed):
+    from comp_inference_b200 import _lib
+    Wkn = make_weight(out_f, in_f, seed).t().contiguous().cuda()
+    K, N = in_f, out_f
+    c = ci.compress_weight_cuda(Wkn, 128, 32)
+    for M, splits in ((512, (1, 2, 4, 8)), (2048, (0,))):
+        x = torch.randn(M, K, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).cuda()
+        ref = x.float() @ Wkn.float()
+        for sk in splits:
+            y = ci.fused_rans_linear_triton(x, weight_shape=(K, N), SPLIT_K=sk, **_linear_args(c))
+            err = float((y.float() - ref).abs().max() / ref.abs().max())
+            assert err <= REL_TOL, (M, sk, err)
+    assert _lib.kernel_status(x.device) == 0
