@@ -33,11 +33,14 @@ constexpr uint32_t kBK = 64;               // k per shared-memory sub-tile: 64 b
 constexpr uint32_t kTileH = 128;           // tile height this kernel is specialised for (2 sub-tiles per tile row)
 constexpr uint32_t kASub = kBN * kBK * 2;  // 16 KB
 constexpr uint32_t kAStage = 2 * kASub;    // 32 KB: streams "A" fill sub-tile 0, streams "B" sub-tile 1
-constexpr uint32_t kAStages = 2;
+constexpr uint32_t kAStages = 3;
 constexpr uint32_t kBTile = kBM * kBK * 2; // 32 KB
-constexpr uint32_t kBSlots = 3;
+constexpr uint32_t kBSlots = 2;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kGemmThreads = 192;     // warps 0-3 decode + epilogue, 4 TMA producer, 5 MMA issuer
+constexpr uint32_t kDecGroups = 2;        // two groups of four decode warps work on alternate tile rows
+constexpr uint32_t kDecWarps = 4 * kDecGroups;
+constexpr uint32_t kTmaWarp = kDecWarps, kMmaWarp = kDecWarps + 1;
+constexpr uint32_t kGemmThreads = (kDecWarps + 2) * 32;   // decode + epilogue warps, TMA producer, MMA issuer
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffA = 0;
@@ -49,13 +52,13 @@ constexpr uint32_t kOffStage = kOffBar + kBarRegion;            // per-warp copy
 
 // barrier slots (8 bytes each) inside the barrier region
 enum : uint32_t {
-    kBarFullA = 0,      // [2]  4 arrivals (decode warps)
-    kBarEmptyA = 2,     // [2]  1 arrival  (tcgen05.commit)
-    kBarFullB = 4,      // [3]  1 arrival + bytes (TMA)
-    kBarEmptyB = 7,     // [3]  1 arrival  (tcgen05.commit)
+    kBarFullA = 0,      // [3]  4 arrivals (the decode warps of one group)
+    kBarEmptyA = 3,     // [3]  1 arrival  (tcgen05.commit)
+    kBarFullB = 6,      // [2]  1 arrival + bytes (TMA)
+    kBarEmptyB = 8,     // [2]  1 arrival  (tcgen05.commit)
     kBarAcc = 10,       // [1]  1 arrival  (tcgen05.commit after the last MMA)
-    kBarCopy = 11,      // [4][2] per decode warp, per copy stage
-    kBarCount = 19,
+    kBarCopy = 11,      // [8][2] per decode warp, per copy stage
+    kBarCount = 27,
 };
 constexpr uint32_t kOffTmemPtr = kBarCount * 8;                  // u32: base address from tcgen05.alloc
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;                  // u32: set when a wait ran out
@@ -63,7 +66,7 @@ constexpr uint32_t kOffFlag = kOffAbort + 4;                     // u32: last-ar
 
 struct GemmArgs {
     LinArgs a;
-    uint32_t win_cap, stage_bytes, copy_stages;   // per-warp copy buffers of the decode warps
+    uint32_t win_cap;                             // bytes per copy stage (a tile's compressed byte block); 2 stages per decode warp
     uint32_t m_tiles;                             // ceil(M / 512)
     uint32_t splits, tiles_per_split;             // split-K over tile rows
     uint32_t *status;
@@ -164,13 +167,13 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
         for (uint32_t i = 0; i < kAStages; ++i) { mbar_init(bar(kBarFullA + i), 4); mbar_init(bar(kBarEmptyA + i), 1); }
         for (uint32_t i = 0; i < kBSlots; ++i) { mbar_init(bar(kBarFullB + i), 1); mbar_init(bar(kBarEmptyB + i), 1); }
         mbar_init(bar(kBarAcc), 1);
-        for (uint32_t i = 0; i < 8; ++i) mbar_init(bar(kBarCopy + i), 1);
+        for (uint32_t i = 0; i < 2 * kDecWarps; ++i) mbar_init(bar(kBarCopy + i), 1);
         *s_abort = 0;
         *s_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     load_lut(reinterpret_cast<uint32_t *>(smem + kOffLut), a.lut, a.tables, a.slot_map);
-    if (warp == 5) tmem_alloc(smem_s + kOffBar + kOffTmemPtr, kTmemCols);
+    if (warp == kMmaWarp) tmem_alloc(smem_s + kOffBar + kOffTmemPtr, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -180,34 +183,48 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
         if (lane == 0) { atomicExch(p.status, code); *s_abort = 1; }
     };
 
-    if (warp < 4) {
+    if (warp < kDecWarps) {
         // =========================== decode warps: fill the A stages ===============================
-        const uint32_t grp = nblk * 4 + warp;                            // this warp's 32-column group
+        // Group j (warps 4j..4j+3) decodes tile rows j, j+2, ...; warp q of a group owns 32 columns.
+        const uint32_t grpj = warp >> 2, q = warp & 3;
+        const uint32_t grp = nblk * 4 + q;                               // this warp's 32-column group
         const bool grp_live = grp < g.groups;
         const uint32_t lut_s = smem_s + kOffLut;
-        const uint32_t copy_s = smem_s + kOffStage + warp * (p.copy_stages * p.stage_bytes);
+        const uint32_t copy_s = smem_s + kOffStage + warp * (2 * p.win_cap);
         const uint32_t man_tile = kTileH * 32;
-        const uint32_t nl = warp * 32 + lane;                            // column inside the CTA's 128
+        const uint32_t nl = q * 32 + lane;                               // column inside the CTA's 128
 
-        auto issue = [&](uint32_t tk, uint32_t cs) {                     // bulk copies of unit (tk, grp)
+        auto issue = [&](uint32_t tk, uint32_t cs) {                     // bulk copy of the byte block of unit (tk, grp)
             if (lane != 0 || !grp_live) return;
             const uint32_t t0 = tk * g.tiles_n + grp;                    // tile width 32: one tile per unit
-            const uint32_t begin = a.tile_offsets[t0];
             uint32_t wbytes = a.tile_max_lens[t0] * 64u;
             if (wbytes > p.win_cap) { atomicExch(p.status, 2u); wbytes = 0; }
-            const uint32_t b = bar(kBarCopy + warp * 2 + cs), dst = copy_s + cs * p.stage_bytes;
+            const uint32_t b = bar(kBarCopy + warp * 2 + cs);
             fence_async_proxy();
-            mbar_expect_tx(b, wbytes + man_tile);
-            if (wbytes) bulk_load(dst, a.stream + begin, wbytes, b);
-            bulk_load(dst + p.win_cap, a.mantissa + (size_t)t0 * man_tile, man_tile, b);
+            if (wbytes) {
+                mbar_expect_tx(b, wbytes);
+                bulk_load(copy_s + cs * p.win_cap, a.stream + a.tile_offsets[t0], wbytes, b);
+            } else {
+                mbar_arrive(b);                                          // nothing to copy: complete the phase by hand
+            }
+        };
+        // sign+mantissa bytes of eight rows of both halves, straight from global memory (L2/L1), fetched one
+        // pass ahead of their use so their latency never sits on the decode chain
+        auto load_man = [&](const uint8_t *mg, uint32_t i0, uint32_t (&m)[16]) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                m[r] = __ldg(mg + (i0 + r) * 32);
+                m[8 + r] = __ldg(mg + (64 + i0 + r) * 32);
+            }
         };
 
         uint32_t copy_parity[2] = {0, 0};
-        if (n_iters) issue(k_begin, 0);
-        for (uint32_t it = 0; it < n_iters && !*s_abort; ++it) {
-            const uint32_t tk = k_begin + it, s = it % kAStages, cs = p.copy_stages == 2 ? (it & 1) : 0;
-            if (p.copy_stages == 2 && it + 1 < n_iters) issue(tk + 1, cs ^ 1);
-            // the stage must have been drained by the MMAs that read it two iterations ago
+        if (grpj < n_iters) issue(k_begin + grpj, 0);
+        uint32_t li = 0;
+        for (uint32_t it = grpj; it < n_iters && !*s_abort; it += kDecGroups, ++li) {
+            const uint32_t tk = k_begin + it, s = it % kAStages, cs = li & 1;
+            if (it + kDecGroups < n_iters) issue(tk + kDecGroups, cs ^ 1);
+            // the stage must have been drained by the MMAs that read it kAStages iterations ago
             if (!mbar_wait_warp(bar(kBarEmptyA + s), ((it / kAStages) & 1) ^ 1)) { give_up(3); break; }
             const uint32_t a0_s = smem_s + kOffA + s * kAStage, a1_s = a0_s + kASub;
             if (!grp_live) {                                             // columns beyond N: zeros
@@ -217,73 +234,85 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
                 }
             } else {
                 const uint32_t t0 = tk * g.tiles_n + grp;
+                const uint8_t *mg = a.mantissa + (size_t)t0 * man_tile + lane;
+                const uint32_t row0 = tk * kTileH, remain = g.K - row0;
+                const uint32_t nA = min(remain, 64u), nB = remain > 64u ? min(remain - 64u, 64u) : 0;
+                const bool full_tile = nB == 64;
+                uint32_t m0r[16], m1r[16];
+                if (full_tile) load_man(mg, 0, m0r);
                 uint32_t stA = a.states[(size_t)t0 * 64 + lane], stB = a.states[(size_t)t0 * 64 + 32 + lane];
                 const uint32_t ml = a.tile_max_lens[t0];
                 if (!mbar_wait_warp(bar(kBarCopy + warp * 2 + cs), copy_parity[cs])) { give_up(4); break; }
                 copy_parity[cs] ^= 1;
-                const uint32_t win_s = copy_s + cs * p.stage_bytes;
-                const uint32_t man_s = win_s + p.win_cap + lane;
+                const uint32_t win_s = copy_s + cs * p.win_cap;
                 uint32_t posA = win_s + lane + (ml - 1) * 64u, posB = posA + 32;   // an empty tile starts one row below
-                const uint32_t row0 = tk * kTileH, remain = g.K - row0;
-                const uint32_t nA = min(remain, 64u), nB = remain > 64u ? min(remain - 64u, 64u) : 0;
-#pragma unroll 1
-                for (uint32_t c = 0; c < 8; ++c) {                       // eight k rows of both halves per pass
+
+                // one pass = eight k rows of both halves -> one 16-byte chunk in each sub-tile
+                auto pass = [&](uint32_t c, const uint32_t (&m)[16]) {
                     uint32_t pa[4], pb[4];
-                    const uint32_t i0 = c * 8;
-                    if (i0 + 8 <= nB) {
-                        const uint32_t mA = man_s + i0 * 32, mB = mA + 64 * 32;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t ma0 = lds_u8(mA + (2 * j) * 32), ma1 = lds_u8(mA + (2 * j + 1) * 32);
-                            const uint32_t mb0 = lds_u8(mB + (2 * j) * 32), mb1 = lds_u8(mB + (2 * j + 1) * 32);
-                            uint32_t ba = lds_u8(posA), bb = lds_u8(posB);
-                            const uint32_t e0 = decode_fast(stA, lut_s);
-                            const uint32_t f0 = decode_fast(stB, lut_s);
-                            renorm_spec<64>(stA, posA, ba);
-                            renorm_spec<64>(stB, posB, bb);
-                            ba = lds_u8(posA);
-                            bb = lds_u8(posB);
-                            const uint32_t e1 = decode_fast(stA, lut_s);
-                            const uint32_t f1 = decode_fast(stB, lut_s);
-                            renorm_spec<64>(stA, posA, ba);
-                            renorm_spec<64>(stB, posB, bb);
-                            pa[j] = weight_pair(e0, e1, ma0, ma1);
-                            pb[j] = weight_pair(f0, f1, mb0, mb1);
-                        }
-                    } else {                                             // ragged last tile row: zeros beyond K
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t ba = lds_u8(posA), bb = lds_u8(posB);
+                        const uint32_t e0 = decode_fast(stA, lut_s);
+                        const uint32_t f0 = decode_fast(stB, lut_s);
+                        renorm_spec<64>(stA, posA, ba);
+                        renorm_spec<64>(stB, posB, bb);
+                        ba = lds_u8(posA);
+                        bb = lds_u8(posB);
+                        const uint32_t e1 = decode_fast(stA, lut_s);
+                        const uint32_t f1 = decode_fast(stB, lut_s);
+                        renorm_spec<64>(stA, posA, ba);
+                        renorm_spec<64>(stB, posB, bb);
+                        pa[j] = weight_pair(e0, e1, m[2 * j], m[2 * j + 1]);
+                        pb[j] = weight_pair(f0, f1, m[8 + 2 * j], m[8 + 2 * j + 1]);
+                    }
+                    sts_v4(a0_s + a_chunk_offset(nl, c), pa[0], pa[1], pa[2], pa[3]);
+                    sts_v4(a1_s + a_chunk_offset(nl, c), pb[0], pb[1], pb[2], pb[3]);
+                };
+                if (full_tile) {
+#pragma unroll 1
+                    for (uint32_t c = 0; c < 8; c += 2) {
+                        load_man(mg, (c + 1) * 8, m1r);
+                        pass(c, m0r);
+                        if (c + 2 < 8) load_man(mg, (c + 2) * 8, m0r);
+                        pass(c + 1, m1r);
+                    }
+                } else {                                                 // ragged last tile row: zeros beyond K
+#pragma unroll 1
+                    for (uint32_t c = 0; c < 8; ++c) {
+                        uint32_t pa[4], pb[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             uint32_t h[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                const uint32_t i = i0 + 2 * j + q;
+                            for (int qq = 0; qq < 2; ++qq) {
+                                const uint32_t i = c * 8 + 2 * j + qq;
                                 if (i < nA) {
                                     const uint32_t e = decode_fast(stA, lut_s);
                                     renorm_fast<64>(stA, posA);
                                     renorm_fast<64>(stA, posA);
-                                    h[q] = weight_bits(e, lds_u8(man_s + i * 32));
+                                    h[qq] = weight_bits(e, __ldg(mg + i * 32));
                                 }
                                 if (i < nB) {
                                     const uint32_t e = decode_fast(stB, lut_s);
                                     renorm_fast<64>(stB, posB);
                                     renorm_fast<64>(stB, posB);
-                                    h[2 + q] = weight_bits(e, lds_u8(man_s + (64 + i) * 32));
+                                    h[2 + qq] = weight_bits(e, __ldg(mg + (64 + i) * 32));
                                 }
                             }
                             pa[j] = h[0] | (h[1] << 16);
                             pb[j] = h[2] | (h[3] << 16);
                         }
+                        sts_v4(a0_s + a_chunk_offset(nl, c), pa[0], pa[1], pa[2], pa[3]);
+                        sts_v4(a1_s + a_chunk_offset(nl, c), pb[0], pb[1], pb[2], pb[3]);
                     }
-                    sts_v4(a0_s + a_chunk_offset(nl, c), pa[0], pa[1], pa[2], pa[3]);
-                    sts_v4(a1_s + a_chunk_offset(nl, c), pb[0], pb[1], pb[2], pb[3]);
                 }
-                if (p.copy_stages == 1 && it + 1 < n_iters) { __syncwarp(); issue(tk + 1, 0); }
             }
             fence_async_proxy();                                         // generic writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kBarFullA + s));
         }
-    } else if (warp == 4) {
+    } else if (warp == kTmaWarp) {
         // =========================== TMA producer: activation tiles ================================
         uint32_t cnt = 0;
         for (uint32_t it = 0; it < n_iters && !*s_abort; ++it) {
@@ -332,17 +361,18 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
     }
 
     // ---- epilogue: the four decode warps read the accumulators out of tensor memory ----------------
-    if (warp < 4) {
+    if (warp < kDecWarps) {
         bool ok = !*s_abort;
         if (ok && !mbar_wait_warp(bar(kBarAcc), 0)) { give_up(8); ok = false; }
         if (ok) {
             tc_fence_after();
-            const uint32_t n = nblk * kBN + warp * 32 + lane;            // accumulator row = weight column
+            const uint32_t q = warp & 3, half = warp >> 2;               // a warp may only touch tensor-memory lanes 32*(warp%4)..
+            const uint32_t n = nblk * kBN + q * 32 + lane;               // accumulator row = weight column
             const float bias = (a.bias && n < g.N && p.splits == 1) ? load_bf16(a.bias + n) : 0.f;
             for (uint32_t mc = 0; mc < chunks; ++mc)
-                for (uint32_t cc = 0; cc < kBM / 32; ++cc) {
+                for (uint32_t cc = half; cc < kBM / 32; cc += kDecGroups) {
                     uint32_t v[32];
-                    tmem_ld32(tmem_base + ((warp * 32u) << 16) + mc * kBM + cc * 32, v);
+                    tmem_ld32(tmem_base + ((q * 32u) << 16) + mc * kBM + cc * 32, v);
                     const uint32_t mb = m0 + mc * kBM + cc * 32;
                     if (n < g.N) {
 #pragma unroll
@@ -361,20 +391,68 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
         // deterministic split-K: the CTA that arrives last adds the partials in split order
         uint32_t *ticket = a.tickets + (mtile * gridDim.x + nblk);
         if (last_arrival(ticket, p.splits, s_flag)) {
-            for (uint32_t idx = threadIdx.x; idx < m_here * kBN; idx += blockDim.x) {
-                const uint32_t m = m0 + idx / kBN, n = nblk * kBN + idx % kBN;
-                if (n >= g.N) continue;
-                float v = 0.f;
-                for (uint32_t s = 0; s < p.splits; ++s) v += __ldcg(a.partial + ((size_t)s * a.M + m) * g.N + n);
-                if (a.bias) v += load_bf16(a.bias + n);
-                a.y[(size_t)m * a.ldy + n] = float_to_bf16_bits(v);
+            // Four consecutive columns per thread, four rows per pass, all splits loaded before the first add:
+            // up to 32 independent 16-byte loads in flight per thread instead of one L2 round trip per term.
+            const bool vec = (g.N & 3u) == 0 && (a.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 7u) == 0;
+            const uint32_t quads = kBN / 4, items = m_here * quads;
+            for (uint32_t base = threadIdx.x; base < items; base += 4 * blockDim.x) {
+                float4 acc4[4];
+                float4 t[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t idx = base + u * blockDim.x;
+                    const uint32_t m = m0 + idx / quads, n = nblk * kBN + (idx % quads) * 4;
+                    const bool in = idx < items && n < g.N;
+#pragma unroll
+                    for (int sidx = 0; sidx < 8; ++sidx) {
+                        t[u][sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (in && (uint32_t)sidx < p.splits) {
+                            const float *src = a.partial + ((size_t)sidx * a.M + m) * g.N + n;
+                            if (vec) t[u][sidx] = __ldcg(reinterpret_cast<const float4 *>(src));
+                            else {
+                                t[u][sidx].x = __ldcg(src);
+                                if (n + 1 < g.N) t[u][sidx].y = __ldcg(src + 1);
+                                if (n + 2 < g.N) t[u][sidx].z = __ldcg(src + 2);
+                                if (n + 3 < g.N) t[u][sidx].w = __ldcg(src + 3);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    acc4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int sidx = 0; sidx < 8; ++sidx) {              // fixed split order
+                        acc4[u].x += t[u][sidx].x; acc4[u].y += t[u][sidx].y;
+                        acc4[u].z += t[u][sidx].z; acc4[u].w += t[u][sidx].w;
+                    }
+                    const uint32_t idx = base + u * blockDim.x;
+                    if (idx >= items) continue;
+                    const uint32_t m = m0 + idx / quads, n = nblk * kBN + (idx % quads) * 4;
+                    const float v[4] = {acc4[u].x, acc4[u].y, acc4[u].z, acc4[u].w};
+                    uint16_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float f = v[e];
+                        if (a.bias && n + e < g.N) f += load_bf16(a.bias + n + e);
+                        o[e] = float_to_bf16_bits(f);
+                    }
+                    uint16_t *dst = a.y + (size_t)m * a.ldy + n;
+                    if (vec && n + 3 < g.N) {
+                        *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (n + e < g.N) dst[e] = o[e];
+                    }
+                }
             }
             if (threadIdx.x == 0) *ticket = 0;
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem_base, kTmemCols);
+    if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // ------------------------------------------------------------------------------------------ host
@@ -422,19 +500,18 @@ int launch_linear_gemm(const LinArgs &a, uint32_t max_tile_len, size_t partial_c
     GemmArgs p;
     p.a = a;
     p.win_cap = ((max_tile_len * 64u + 15u) & ~15u) + 16u;
-    p.stage_bytes = p.win_cap + kTileH * 32u;
     int dev = 0, max_smem = 0;
     CI_CUDA(cudaGetDevice(&dev));
     CI_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
     const uint32_t fixed = kOffStage + 1024;                             // + alignment slack
-    if ((uint32_t)max_smem < fixed + 4 * p.stage_bytes) return 1;
-    p.copy_stages = ((uint32_t)max_smem >= fixed + 8 * p.stage_bytes) ? 2 : 1;
-    const size_t smem = fixed + (size_t)4 * p.copy_stages * p.stage_bytes;
+    const size_t smem = fixed + (size_t)kDecWarps * 2 * p.win_cap;
+    if ((size_t)max_smem < smem) return 1;
 
     p.m_tiles = (a.M + kBM * kMChunks - 1) / (kBM * kMChunks);
     const uint32_t n_blocks = (g.N + kBN - 1) / kBN;
     uint32_t splits = split_k ? split_k : gemm_splits(a.M, g.N, g.tiles_k);
     if (splits > g.tiles_k) splits = g.tiles_k;
+    if (splits > 8) splits = 8;                                       // the final reduction holds at most 8 partials
     while (splits > 1 && (size_t)splits * a.M * g.N * sizeof(float) > partial_capacity) --splits;
     p.tiles_per_split = (g.tiles_k + splits - 1) / splits;
     p.splits = (g.tiles_k + p.tiles_per_split - 1) / p.tiles_per_split;

@@ -171,21 +171,42 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
         last = __shfl_sync(kFull, last, 0);
         if (!last) return;
         __threadfence();
+        // All loads of a batch of four partials are issued before any of them is used: a plain running
+        // sum would wait one L2 round trip per partial (16 in a row for a 4096-row matrix).
+        float sum[4][4];
+#pragma unroll
+        for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sum[nb][j] = 0.f;
+        const bool has0 = r0 < a.M, has1 = r0 + 8 < a.M;
+        for (uint32_t w0 = first_w; w0 <= last_w; w0 += 4) {
+            float2 t[4][4][2];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const bool in = w0 + q <= last_w;
+                const float *src = a.partial + (size_t)(w0 + q + grp) * a.M * 32 + c0;
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) {
+                    t[q][nb][0] = (in && has0) ? __ldcg(reinterpret_cast<const float2 *>(src + r0 * 32 + nb * 8))
+                                               : make_float2(0.f, 0.f);
+                    t[q][nb][1] = (in && has1) ? __ldcg(reinterpret_cast<const float2 *>(src + (r0 + 8) * 32 + nb * 8))
+                                               : make_float2(0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)                         // fixed order: partial w0, w0+1, ...
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) {
+                    sum[nb][0] += t[q][nb][0].x;
+                    sum[nb][1] += t[q][nb][0].y;
+                    sum[nb][2] += t[q][nb][1].x;
+                    sum[nb][3] += t[q][nb][1].y;
+                }
+        }
 #pragma unroll
         for (int nb = 0; nb < 4; ++nb) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t m = r0 + 8 * h;
-                if (m >= a.M) continue;
-                float v0 = 0.f, v1 = 0.f;
-                for (uint32_t w = first_w; w <= last_w; ++w) {
-                    float2 v = __ldcg(reinterpret_cast<const float2 *>(a.partial + (size_t)(w + grp) * a.M * 32 + m * 32 +
-                                                                         nb * 8 + c0));
-                    v0 += v.x;
-                    v1 += v.y;
-                }
-                store_y(m, grp * 32 + nb * 8 + c0, v0, v1);
-            }
+            store_y(r0, grp * 32 + nb * 8 + c0, sum[nb][0], sum[nb][1]);
+            store_y(r0 + 8, grp * 32 + nb * 8 + c0, sum[nb][2], sum[nb][3]);
         }
         __syncwarp();
         if (lane == 0) a.tickets[grp] = 0;                      // ready for the next call
