@@ -77,23 +77,28 @@ __device__ __forceinline__ uint32_t decode_fast(uint32_t &state, uint32_t lut_s)
     state = (e >> 20) * (state >> kProbBits) + (e & 0xFFFu);
     return e;
 }
-// Renormalisation, STRIDE bytes between the rows of a stream.  The first byte is loaded before the
-// state update is known to need it (its address does not depend on the new state, and some lane of
-// the warp needs it on nearly every step anyway), which takes one shared-memory latency off the
-// decode chain; the improbable second byte stays predicated.  No lower-bound test: a well-formed
-// stream always has a byte left when its state is below 2^16, and the launcher guarantees enough
-// mapped shared memory below every window that a malformed stream reads garbage instead of faulting.
+// Renormalisation, STRIDE bytes between the rows of a stream.
+//
+// No lower-bound test anywhere in this family: a well-formed stream always has a byte left when its
+// state is below 2^16, and the launchers guarantee enough mapped shared memory below every window
+// that a malformed stream reads garbage instead of faulting.
+//
+// renorm_spec: exact.  The first byte is loaded by the caller before the state update is known to
+// need it (its address does not depend on the new state, and some lane of the warp needs it on
+// nearly every step anyway), which takes one shared-memory latency off the decode chain.  A second
+// byte is needed exactly when the state before renormalisation is below 2^8, so its test and load
+// do not wait for the first byte either.
 template <uint32_t STRIDE>
 __device__ __forceinline__ void renorm_spec(uint32_t &state, uint32_t &pos, uint32_t first) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .u32 b;\n\t"
-        "setp.lt.u32 p, %0, 65536;\n\t"
-        "@p mad.lo.u32 %0, %0, 256, %2;\n\t"
-        "@p sub.u32 %1, %1, %3;\n\t"
-        "setp.lt.u32 p, %0, 65536;\n\t"
-        "@p ld.shared.u8 b, [%1];\n\t"
-        "@p mad.lo.u32 %0, %0, 256, b;\n\t"
-        "@p sub.u32 %1, %1, %3;\n\t}"
+        "{\n\t.reg .pred p1, p2;\n\t.reg .u32 b;\n\t"
+        "setp.lt.u32 p1, %0, 65536;\n\t"
+        "setp.lt.u32 p2, %0, 256;\n\t"
+        "@p2 ld.shared.u8 b, [%1+-%3];\n\t"
+        "@p1 mad.lo.u32 %0, %0, 256, %2;\n\t"
+        "@p1 sub.u32 %1, %1, %3;\n\t"
+        "@p2 mad.lo.u32 %0, %0, 256, b;\n\t"
+        "@p2 sub.u32 %1, %1, %3;\n\t}"
         : "+r"(state), "+r"(pos)
         : "r"(first), "n"(STRIDE));
 }

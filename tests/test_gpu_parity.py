@@ -376,3 +376,22 @@ def test_prefill_gemm_llama_shapes(ci, out_f, in_f, seed):
             err = float((y.float() - ref).abs().max() / ref.abs().max())
             assert err <= REL_TOL, (M, sk, err)
     assert _lib.kernel_status(x.device) == 0
+
+
+@pytest.mark.parametrize("M", [1, 7, 512])
+def test_fused_linear_wide_exponent_spread(ci, M):
+    """Weights whose exponents spread over many octaves: improbable symbols (two renormalisation bytes,
+    the verify-and-redo path of the staged kernels) occur in almost every tile."""
+    K, N = 2048, 512
+    g = torch.Generator().manual_seed(99)
+    W = (torch.randn(K, N, generator=g) * torch.exp(torch.randn(K, N, generator=g) * 3.0) * 0.02).to(torch.bfloat16).cuda()
+    c = ci.compress_weight_cuda(W, 128, 32)
+    a = _linear_args(c)
+    w = ci.rans_decompress_bf16(a["compressed_data"], a["initial_states"], a["tables"], a["slot_map"], (K, N),
+                                a["tile_offsets"], a["tile_max_lens"], 128, 32, a["mantissas"])
+    assert torch.equal(w.view(torch.uint16), W.view(torch.uint16))
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16).cuda()
+    y = ci.fused_rans_linear_triton(x, weight_shape=(K, N), SPLIT_K=0, **a)
+    ref = x.float() @ W.float()
+    err = float((y.float() - ref).abs().max() / ref.abs().max())
+    assert err <= REL_TOL, err
