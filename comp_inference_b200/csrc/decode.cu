@@ -9,20 +9,13 @@
 // with 16-byte loads before decoding, so renormalisation never touches global
 // memory.  Tiles whose byte block does not fit the window fall back to cached
 // global byte loads inside the same kernel.
-#include "common.cuh"
+#include "decode.cuh"
 
 namespace ci {
 
 constexpr int kDecWarps = 8;           // warps per CTA
 constexpr uint32_t kStageBytes = 4096; // per-warp window for compressed bytes
 
-struct DecArgs {
-    const uint8_t *stream;
-    const uint32_t *states, *tables, *tile_offsets, *tile_max_lens, *lut;
-    const uint8_t *slot_map, *mantissa;
-    Geom g;
-    uint32_t stream_aligned;   // stream pointer is 16-byte aligned
-};
 
 // Lane-level description of one 32-column task.
 struct LaneTask {
@@ -218,6 +211,8 @@ static int decode_tiled(const ci_tiled_weight *w, void *d_out, cudaStream_t s) {
     if (rc) return rc;
     CI_REQUIRE(d_out != nullptr, "null output");
     DecArgs a = make_args(w);
+    rc = launch_decode_staged(a, w->max_tile_len, BF16, d_out, s);   // staged path when the tensor qualifies
+    if (rc <= 0) return rc;
     uint32_t n_tasks = a.g.tiles_k * a.g.groups;
     size_t smem = kProbScale * 4 + (size_t)kDecWarps * kStageBytes;
     static bool attr_set[2] = {false, false};

@@ -41,7 +41,7 @@ def rans_decomp_triton_tiled(compressed_streams, initial_states, tables, slot_ma
     """Exponent plane uint8 [K,N] of a tiled stream."""
     K, N = int(output_shape[0]), int(output_shape[1])
     w, keep = _lib.tiled_weight(compressed_streams, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
-                                None, K, N, int(tile_k), int(tile_n))
+                                None, K, N, int(tile_k), int(tile_n), want_max=True)
     out = torch.empty((K, N), device=compressed_streams.device, dtype=torch.uint8)
     _lib.check(_lib.load().ci_decode_plane(w, _lib.ptr(out), _lib.stream()))
     return out
@@ -53,7 +53,7 @@ def rans_decompress_bf16(compressed_streams, initial_states, tables, slot_map, w
     chain of rans_decompress_module_weight_bf16 (comp_inference/comp_inference.py:633-711)."""
     K, N = int(weight_shape[0]), int(weight_shape[1])
     w, keep = _lib.tiled_weight(compressed_streams, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
-                                mantissas, K, N, int(tile_k), int(tile_n))
+                                mantissas, K, N, int(tile_k), int(tile_n), want_max=True)
     out = torch.empty((K, N), device=compressed_streams.device, dtype=torch.bfloat16)
     _lib.check(_lib.load().ci_decode_bf16(w, _lib.ptr(out), _lib.stream()))
     return out
