@@ -27,6 +27,12 @@ from .ops import (  # noqa: F401
     rans_decompress_bf16,
     triton_matmul,
 )
+from .rans_saving import (  # noqa: F401
+    compress_model,
+    load_compressed_model,
+    pack_and_save_tensors,
+    save_rans_model_package,
+)
 from .pytorch_runtime import (  # noqa: F401
     RansEmbedding,
     RansLinear,
