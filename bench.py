@@ -152,6 +152,43 @@ def block_step(mods, x, world):
     return y
 
 
+def secondary_metrics(mods, device):
+    """The other two halves of the headline metric on the same block, N = 1 only, short runs outside the
+    timed region: stand-alone rANS decode (effective uncompressed GB/s) and prefill through the tcgen05
+    decode-GEMM (tokens/s at 512 activation rows)."""
+    import comp_inference_b200 as ci
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def decode_all():
+        for m in mods.values():
+            ci.rans_decompress_bf16(m.rans_exp_stream, m.rans_exp_states, m.rans_exp_tables, m.rans_exp_slot_map,
+                                    (m.in_features, m.out_features), m.rans_exp_tile_offsets,
+                                    m.rans_exp_tile_max_lens, m.tile_k, m.tile_n, m.rans_man_raw)
+
+    dense_bytes = sum(2 * m.in_features * m.out_features for m in mods.values())
+    ms = timed(decode_all, 10)
+    peak, src = peaks()
+    out = {"decode_bf16": {"effective_uncompressed_GBs": dense_bytes / (ms * 1e-3) / 1e9, "ms_per_block": ms,
+                           "frac_of_hbm_peak": dense_bytes / (ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}"}}
+    x = torch.randn(512, HIDDEN, generator=torch.Generator().manual_seed(2512)).to(torch.bfloat16).to(device)
+    ms = timed(lambda: block_step(mods, x, 1), 10)
+    flops = sum(2.0 * 512 * m.in_features * m.out_features for m in mods.values())
+    out["prefill_M512"] = {"tok_s": 512 / (ms * 1e-3), "ms_per_block": ms, "TFLOPs": flops / (ms * 1e-3) / 1e12,
+                           "kernel": "k_linear_gemm (tcgen05.mma, TMEM accumulators)"}
+    return out
+
+
 def cpu_baseline_run(M, steps, warmup):
     """Decode + matmul of the same block with the CPU oracle on all host cores; returns (tok/s, ms/step, cores)."""
     from oracle import oracle as O
@@ -314,6 +351,8 @@ def run_ours(args):
                              "effective_uncompressed_GBs": sum(2 * K * N for _, K, N, _, _ in LAYERS) / world
                              / (dev_ms * 1e-3) / 1e9},
                 "clocks": clocks, "notes": notes}
+        if world == 1:
+            line["extra"] = secondary_metrics(mods, device)
         if world == 1 and not args.no_cpu:
             val, ms, cores = cpu_baseline_run(M, 1, 1)
             line["cpu_baseline"] = {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
