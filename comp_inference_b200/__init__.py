@@ -33,6 +33,7 @@ from .rans_saving import (  # noqa: F401
     pack_and_save_tensors,
     save_rans_model_package,
 )
+from .rans_gguf import hf_to_gguf_name, read_rans_gguf, save_rans_model_gguf  # noqa: F401
 from .pytorch_runtime import (  # noqa: F401
     RansEmbedding,
     RansLinear,
