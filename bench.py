@@ -344,7 +344,7 @@ def run_ours(args):
                 "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
                 "gpu_launches": launches * args.steps,
-                "roofline": {"bound": "hbm", "kernel": "k_linear_mma", "achieved": achieved, "peak": peak,
+                "roofline": {"bound": "hbm", "kernel": "k_linear_mma4", "achieved": achieved, "peak": peak,
                              "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {src}",
                              "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": traffic,
                              "algorithmic_bytes_per_launch": algo / launches,

@@ -383,6 +383,9 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
         // staged tensor-core kernel when the weight qualifies (tile width <= 32, known maximum tile
         // depth, aligned buffers, a workspace); split_k != 0 asks for the generic split-K kernel
         if (split_k == 0 && have_ws) {
+            rc = launch_linear_mma4(a, w->max_tile_len, s);     // 32-wide tiles, whole tile rows
+            if (rc == CI_OK) continue;
+            if (rc < 0) return rc;
             rc = launch_linear_mma(a, w->max_tile_len, s);
             if (rc == CI_OK) continue;
             if (rc < 0) return rc;

@@ -124,6 +124,8 @@ __device__ __forceinline__ bool last_arrival(uint32_t *ticket, uint32_t expected
 // Staged tensor-core path (linear_mma.cu).  Returns CI_OK when it launched, 1 when the
 // weight does not qualify (the caller then uses the generic kernel), < 0 on error.
 int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s);
+// Register-direct variant for 32-wide tiles and K a multiple of the tile height (linear_mma4.cu).
+int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s);
 
 // tcgen05 decode-GEMM for many activation rows (gemm_sm100.cu); same return convention.
 // partial_capacity = bytes available behind a.partial for split-K partial sums.

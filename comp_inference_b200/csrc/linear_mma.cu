@@ -29,7 +29,7 @@ constexpr uint32_t kWtBytes = 2048;          // two swizzled 32x16 bf16 tiles (A
 struct MmaArgs {
     LinArgs a;
     uint32_t win_cap;      // bytes reserved per stage for the compressed byte block
-    uint32_t stage_bytes;  // win_cap + mantissa block
+    uint32_t stage_bytes;  // win_cap + mantissa block + the unit's 64 initial states
     uint32_t warp_bytes;   // 2 stages + transpose tiles
     uint32_t per_warp;     // units per warp
     uint32_t total;        // units in the matrix
@@ -84,31 +84,46 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
     const uint32_t wt_s = wbase_s + 2 * p.stage_bytes;
     const uint32_t bar_base = smem_s + kLutBytes + warp * 16;
     const uint32_t man_tile = g.th * TW;
+    const uint32_t st_off = p.win_cap + g.th * 32u;             // initial states inside a stage
 
     const uint32_t gw = blockIdx.x * W + warp;                  // this warp's rank in the grid
     const uint32_t lo = gw * p.per_warp;
     const uint32_t hi = min(lo + p.per_warp, p.total);
 
-    // Queues the two bulk copies of unit t into `stage`.
-    auto issue = [&](uint32_t t, uint32_t stage) {
+    // Byte ranges of this warp's units, 32 at a time: lane j holds unit dbase + j.  All lanes load in
+    // parallel, one unit ahead of the copy that needs them, so no metadata load sits on a unit's start.
+    uint32_t d_begin = 0, d_end = 0, dbase = lo;
+    auto load_desc = [&]() {
+        const uint32_t u = dbase + lane;
+        if (u >= hi) return;
+        const uint32_t grp = u / g.tiles_k, tk = u - grp * g.tiles_k;
+        const uint32_t tn0 = grp * TPG;
+        const uint32_t nt = min(TPG, g.tiles_n - tn0);
+        const uint32_t t0 = tk * g.tiles_n + tn0, tl = t0 + nt - 1;
+        d_begin = __ldg(a.tile_offsets + t0);
+        d_end = __ldg(a.tile_offsets + tl) + __ldg(a.tile_max_lens + tl) * WB;
+    };
+
+    // Queues the three bulk copies of unit t (byte block, sign+mantissa block, initial states) into `stage`.
+    auto issue = [&](uint32_t t, uint32_t stage, uint32_t begin, uint32_t end) {
         if (lane != 0) return;
         const uint32_t grp = t / g.tiles_k, tk = t - grp * g.tiles_k;
         const uint32_t tn0 = grp * TPG;
         const uint32_t nt = min(TPG, g.tiles_n - tn0);
-        const uint32_t t0 = tk * g.tiles_n + tn0, tl = t0 + nt - 1;
-        const uint32_t begin = a.tile_offsets[t0];
-        uint32_t wbytes = a.tile_offsets[tl] + a.tile_max_lens[tl] * WB - begin;
+        const uint32_t t0 = tk * g.tiles_n + tn0;
+        uint32_t wbytes = end - begin;
         if (wbytes > p.win_cap) {                               // metadata disagrees with the declared maximum
             atomicExch(p.status, 2u);
             wbytes = 0;
         }
-        const uint32_t mbytes = nt * man_tile;
+        const uint32_t mbytes = nt * man_tile, sbytes = nt * WB * 4;
         const uint32_t bar = bar_base + stage * 8;
         const uint32_t dst = wbase_s + stage * p.stage_bytes;
         fence_async_proxy();
-        mbar_expect_tx(bar, wbytes + mbytes);
+        mbar_expect_tx(bar, wbytes + mbytes + sbytes);
         if (wbytes) bulk_load(dst, a.stream + begin, wbytes, bar);
         bulk_load(dst + p.win_cap, a.mantissa + (size_t)t0 * man_tile, mbytes, bar);
+        bulk_load(dst + st_off, a.states + (size_t)t0 * WB, sbytes, bar);
     };
 
     // The first copy is started before the table is loaded so both latencies overlap.
@@ -118,7 +133,9 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    if (lo < hi) issue(lo, 0);
+    load_desc();
+    uint32_t nx_begin = __shfl_sync(kFull, d_begin, 0), nx_end = __shfl_sync(kFull, d_end, 0);
+    if (lo < hi) issue(lo, 0, nx_begin, nx_end);
     load_lut(s_lut, a.lut, a.tables, a.slot_map);
     __syncthreads();
     if (lo >= hi) return;                                       // no CTA-wide synchronisation below this line
@@ -171,6 +188,37 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
         last = __shfl_sync(kFull, last, 0);
         if (!last) return;
         __threadfence();
+        if (a.M <= 2) {
+            // One or two activation rows: lane = column, up to sixteen partials of both rows in flight at
+            // once, so the whole reduction of a 4096-row matrix costs one L2 round trip.  Same summation
+            // order as below (partial first_w, first_w + 1, ...).
+            float s0 = 0.f, s1 = 0.f;
+            const bool two = a.M == 2;
+            for (uint32_t w0 = first_w; w0 <= last_w; w0 += 16) {
+                float t0[16], t1[16];
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    const bool in = w0 + q <= last_w;
+                    const float *src = a.partial + (size_t)(w0 + q + grp) * a.M * 32 + lane;
+                    t0[q] = in ? __ldcg(src) : 0.f;
+                    t1[q] = (in && two) ? __ldcg(src + 32) : 0.f;
+                }
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    s0 += t0[q];
+                    s1 += t1[q];
+                }
+            }
+            const uint32_t n = grp * 32 + lane;
+            if (n < g.N) {
+                const float b = a.bias ? load_bf16(a.bias + n) : 0.f;
+                a.y[n] = float_to_bf16_bits(s0 + b);
+                if (two) a.y[(size_t)a.ldy + n] = float_to_bf16_bits(s1 + b);
+            }
+            __syncwarp();
+            if (lane == 0) a.tickets[grp] = 0;
+            return;
+        }
         // All loads of a batch of four partials are issued before any of them is used: a plain running
         // sum would wait one L2 round trip per partial (16 in a row for a 4096-row matrix).
         float sum[4][4];
@@ -232,20 +280,35 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
             zero_acc();
             cur_grp = grp;
         }
-        if (t + 1 < hi) issue(t + 1, stage ^ 1);
+        const uint32_t cur_begin = nx_begin, cur_end = nx_end;
+        if (t + 1 < hi) {
+            if (t + 1 - dbase == 32) {
+                dbase = t + 1;
+                load_desc();
+            }
+            nx_begin = __shfl_sync(kFull, d_begin, t + 1 - dbase);
+            nx_end = __shfl_sync(kFull, d_end, t + 1 - dbase);
+            issue(t + 1, stage ^ 1, nx_begin, nx_end);
+        }
 
         // ---- this lane's two streams ---------------------------------------
-        LaneTile L = lane_tile(a, tk, grp);
-        const uint32_t begin = __shfl_sync(kFull, L.off, 0);
-        const uint32_t t0 = __shfl_sync(kFull, L.t, 0);
-        uint32_t stA = kRansL, stB = kRansL;
-        if (L.live) {
-            stA = a.states[(size_t)L.t * WB + L.lc];
-            stB = a.states[(size_t)L.t * WB + TW + L.lc];
+        LaneTile L;
+        uint32_t t0;
+        if (TW == 32) {                                         // one tile per unit: its range is the unit's
+            L.n = grp * 32 + lane;
+            L.live = L.n < g.N;
+            L.lc = lane;
+            L.t = t0 = tk * g.tiles_n + grp;
+            L.off = cur_begin;
+            L.ml = (cur_end - cur_begin) / WB;
+        } else {
+            L = lane_tile(a, tk, grp);
+            t0 = __shfl_sync(kFull, L.t, 0);
         }
         const uint32_t win_s = wbase_s + stage * p.stage_bytes;
         uint32_t man_s = win_s + p.win_cap + (L.t - t0) * man_tile + L.lc;      // (row 0, this column)
-        uint32_t posA = win_s + (L.off - begin) + L.lc, posB;
+        const uint32_t st_s = win_s + st_off + ((L.t - t0) * WB + L.lc) * 4;
+        uint32_t posA = win_s + (L.off - cur_begin) + L.lc, posB;
         if (L.live) posA += (L.ml - 1) * WB;                    // last byte row; an empty tile starts one row below
         posB = posA + TW;
         const uint32_t row0 = tk * g.th, remain = g.K - row0;
@@ -265,6 +328,12 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
                 stage ^= 1;
                 continue;
             }
+        }
+
+        uint32_t stA = kRansL, stB = kRansL;
+        if (L.live) {
+            stA = lds_u32(st_s);
+            stB = lds_u32(st_s + TW * 4);
         }
 
         // ---- decode 16 rows of each half at a time, multiply on the tensor cores
@@ -368,7 +437,9 @@ static int launch_tw(const MmaArgs &p, uint32_t blocks, uint32_t warps, size_t s
 int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     const Geom &g = a.g;
     if (!(g.tw == 8 || g.tw == 16 || g.tw == 32)) return 1;
-    if ((reinterpret_cast<uintptr_t>(a.stream) & 15u) || (reinterpret_cast<uintptr_t>(a.mantissa) & 15u)) return 1;
+    if ((reinterpret_cast<uintptr_t>(a.stream) & 15u) || (reinterpret_cast<uintptr_t>(a.mantissa) & 15u) ||
+        (reinterpret_cast<uintptr_t>(a.states) & 15u))
+        return 1;
     if (max_tile_len == 0) return 1;                            // unknown: cannot size the byte window
     if (a.M > 16 || (g.th * g.tw) % 16 != 0) return 1;
     // The kernel does not bounds-test stream cursors; a malformed stream can walk at most
@@ -381,7 +452,7 @@ int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     MmaArgs p;
     p.a = a;
     p.win_cap = ((max_tile_len * 64u + 15u) & ~15u) + 16u;
-    p.stage_bytes = p.win_cap + g.th * 32u;
+    p.stage_bytes = p.win_cap + g.th * 32u + 256u;
     p.warp_bytes = 2 * p.stage_bytes + kWtBytes;
     p.warp_bytes = (p.warp_bytes + 127u) & ~127u;
     const uint32_t fixed = kLutBytes + kBarBytes;
