@@ -57,7 +57,9 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 // 4-column sign+mantissa words of those rows.
 template <int C>
 __device__ __forceinline__ uint32_t weight_pair4(uint32_t e_lo, uint32_t e_hi, uint32_t m_lo, uint32_t m_hi) {
-    const uint32_t ee = __byte_perm(e_lo >> 5, e_hi << 11, 0x7610);
+    // Bits 8..23 of each entry side by side: the symbols sit at bits 4..11 / 20..27, three below their
+    // place in a bf16 pair; whatever else the shift drags along is masked out by the bit-select.
+    const uint32_t ee = __byte_perm(e_lo, e_hi, 0x6521) << 3;
     const uint32_t vv = __byte_perm(m_lo, m_hi, 0x4400 + 0x1111 * C);
     return (ee & 0x7F807F80u) | (vv & 0x807F807Fu);
 }
@@ -296,6 +298,22 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
     uint32_t s0, s1, s2, s3, pos0, pos1, pos2, pos3;
     // Four symbols of each of the lane's streams -> four B fragments -> four mma.  m = sign+mantissa words
     // of the four rows, xf = the activations of those rows.
+    // Renormalisation of the four streams.  The first byte (about one symbol in three needs it) is merged
+    // under a predicate; a second byte is needed only after a symbol of frequency below 16, so the whole
+    // warp tests for it with one vote and skips those instructions otherwise.
+    auto renorm4 = [&](uint32_t y0, uint32_t y1, uint32_t y2, uint32_t y3) {
+        const uint32_t lowest = min(min(s0, s1), min(s2, s3));
+        renorm_first<128>(s0, pos0, y0);
+        renorm_first<128>(s1, pos1, y1);
+        renorm_first<128>(s2, pos2, y2);
+        renorm_first<128>(s3, pos3, y3);
+        if (__any_sync(kFull, lowest < 256u)) {
+            renorm_fast<128>(s0, pos0);
+            renorm_fast<128>(s1, pos1);
+            renorm_fast<128>(s2, pos2);
+            renorm_fast<128>(s3, pos3);
+        }
+    };
     auto group = [&](const uint32_t (&m)[4], const uint32_t (&xf)[4]) {
         uint32_t b[4][2];
 #pragma unroll
@@ -305,10 +323,7 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             const uint32_t e1 = decode_fast(s1, lut_s);
             const uint32_t e2 = decode_fast(s2, lut_s);
             const uint32_t e3 = decode_fast(s3, lut_s);
-            renorm_spec<128>(s0, pos0, y0);
-            renorm_spec<128>(s1, pos1, y1);
-            renorm_spec<128>(s2, pos2, y2);
-            renorm_spec<128>(s3, pos3, y3);
+            renorm4(y0, y1, y2, y3);
             y0 = lds_u8(pos0);
             y1 = lds_u8(pos1);
             y2 = lds_u8(pos2);
@@ -317,10 +332,7 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             const uint32_t f1 = decode_fast(s1, lut_s);
             const uint32_t f2 = decode_fast(s2, lut_s);
             const uint32_t f3 = decode_fast(s3, lut_s);
-            renorm_spec<128>(s0, pos0, y0);
-            renorm_spec<128>(s1, pos1, y1);
-            renorm_spec<128>(s2, pos2, y2);
-            renorm_spec<128>(s3, pos3, y3);
+            renorm4(y0, y1, y2, y3);
             b[0][h] = weight_pair4<0>(e0, f0, m[2 * h], m[2 * h + 1]);
             b[1][h] = weight_pair4<1>(e1, f1, m[2 * h], m[2 * h + 1]);
             b[2][h] = weight_pair4<2>(e2, f2, m[2 * h], m[2 * h + 1]);

@@ -102,6 +102,17 @@ __device__ __forceinline__ void renorm_spec(uint32_t &state, uint32_t &pos, uint
         : "+r"(state), "+r"(pos)
         : "r"(first), "n"(STRIDE));
 }
+// First byte only, already loaded by the caller (see renorm_spec); the caller handles a second byte.
+template <uint32_t STRIDE>
+__device__ __forceinline__ void renorm_first(uint32_t &state, uint32_t &pos, uint32_t first) {
+    asm volatile(
+        "{\n\t.reg .pred p1;\n\t"
+        "setp.lt.u32 p1, %0, 65536;\n\t"
+        "@p1 mad.lo.u32 %0, %0, 256, %2;\n\t"
+        "@p1 sub.u32 %1, %1, %3;\n\t}"
+        : "+r"(state), "+r"(pos)
+        : "r"(first), "n"(STRIDE));
+}
 template <uint32_t STRIDE>
 __device__ __forceinline__ void renorm_fast(uint32_t &state, uint32_t &pos) {
     asm volatile(
