@@ -15,7 +15,7 @@
 //     read back with tcgen05.ld for the epilogue.
 // One thread issues the MMAs; mbarriers (full/empty per ring slot, tcgen05.commit for completion)
 // connect the roles.  Grid = (N/128) x ceil(M/512) x split-K; split-K partials are fp32 and are
-// summed in a fixed order by the CTA that draws the last ticket (deterministic).
+// summed in a fixed order (deterministic) by k_splitk_reduce, a chip-wide grid launched right behind.
 //
 // Every wait is bounded: on expiry the role sets the status word, raises a CTA-wide abort flag and
 // falls through to the common exit, where tensor memory is released.
@@ -62,7 +62,6 @@ enum : uint32_t {
 };
 constexpr uint32_t kOffTmemPtr = kBarCount * 8;                  // u32: base address from tcgen05.alloc
 constexpr uint32_t kOffAbort = kOffTmemPtr + 4;                  // u32: set when a wait ran out
-constexpr uint32_t kOffFlag = kOffAbort + 4;                     // u32: last-arrival flag of the split-K ticket
 
 struct GemmArgs {
     LinArgs a;
@@ -153,7 +152,6 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
     auto bar = [&](uint32_t slot) { return bar_s + slot * 8; };
     volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(smem + kOffBar + kOffTmemPtr);
     volatile uint32_t *s_abort = reinterpret_cast<volatile uint32_t *>(smem + kOffBar + kOffAbort);
-    uint32_t *s_flag = reinterpret_cast<uint32_t *>(smem + kOffBar + kOffFlag);
 
     const uint32_t nblk = blockIdx.x, mtile = blockIdx.y, split = blockIdx.z;
     const uint32_t m0 = mtile * (kBM * kMChunks);
@@ -169,7 +167,6 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
         mbar_init(bar(kBarAcc), 1);
         for (uint32_t i = 0; i < 2 * kDecWarps; ++i) mbar_init(bar(kBarCopy + i), 1);
         *s_abort = 0;
-        *s_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     load_lut(reinterpret_cast<uint32_t *>(smem + kOffLut), a.lut, a.tables, a.slot_map);
@@ -178,6 +175,10 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    // Programmatic dependent launch: the set-up above overlapped the previous kernel's tail; activations,
+    // workspace and output may be that kernel's, so wait for it here (no-ops in an ordinary launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     auto give_up = [&](uint32_t code) {
         if (lane == 0) { atomicExch(p.status, code); *s_abort = 1; }
@@ -194,16 +195,29 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
         const uint32_t man_tile = kTileH * 32;
         const uint32_t nl = q * 32 + lane;                               // column inside the CTA's 128
 
-        auto issue = [&](uint32_t tk, uint32_t cs) {                     // bulk copy of the byte block of unit (tk, grp)
+        // Metadata and initial states of a unit are loaded one unit ahead (all of it is small and
+        // L2/HBM resident), so a unit never starts with a dependent global load.
+        struct Unit { uint32_t off, ml, stA, stB; };
+        auto load_unit = [&](uint32_t tk) {
+            Unit u = {0u, 0u, kRansL, kRansL};
+            if (grp_live) {
+                const uint32_t t0 = tk * g.tiles_n + grp;                // tile width 32: one tile per unit
+                u.off = __ldg(a.tile_offsets + t0);
+                u.ml = __ldg(a.tile_max_lens + t0);
+                u.stA = __ldg(a.states + (size_t)t0 * 64 + lane);
+                u.stB = __ldg(a.states + (size_t)t0 * 64 + 32 + lane);
+            }
+            return u;
+        };
+        auto issue = [&](const Unit &u, uint32_t cs) {                   // bulk copy of a unit's byte block
             if (lane != 0 || !grp_live) return;
-            const uint32_t t0 = tk * g.tiles_n + grp;                    // tile width 32: one tile per unit
-            uint32_t wbytes = a.tile_max_lens[t0] * 64u;
+            uint32_t wbytes = u.ml * 64u;
             if (wbytes > p.win_cap) { atomicExch(p.status, 2u); wbytes = 0; }
             const uint32_t b = bar(kBarCopy + warp * 2 + cs);
             fence_async_proxy();
             if (wbytes) {
                 mbar_expect_tx(b, wbytes);
-                bulk_load(copy_s + cs * p.win_cap, a.stream + a.tile_offsets[t0], wbytes, b);
+                bulk_load(copy_s + cs * p.win_cap, a.stream + u.off, wbytes, b);
             } else {
                 mbar_arrive(b);                                          // nothing to copy: complete the phase by hand
             }
@@ -219,11 +233,17 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
         };
 
         uint32_t copy_parity[2] = {0, 0};
-        if (grpj < n_iters) issue(k_begin + grpj, 0);
+        Unit cur = {0u, 0u, kRansL, kRansL}, nxt = cur, nxt2 = cur;
+        if (grpj < n_iters) {
+            cur = load_unit(k_begin + grpj);
+            issue(cur, 0);
+        }
+        if (grpj + kDecGroups < n_iters) nxt = load_unit(k_begin + grpj + kDecGroups);
         uint32_t li = 0;
         for (uint32_t it = grpj; it < n_iters && !*s_abort; it += kDecGroups, ++li) {
             const uint32_t tk = k_begin + it, s = it % kAStages, cs = li & 1;
-            if (it + kDecGroups < n_iters) issue(tk + kDecGroups, cs ^ 1);
+            if (it + kDecGroups < n_iters) issue(nxt, cs ^ 1);
+            if (it + 2 * kDecGroups < n_iters) nxt2 = load_unit(tk + 2 * kDecGroups);
             // the stage must have been drained by the MMAs that read it kAStages iterations ago
             if (!mbar_wait_warp(bar(kBarEmptyA + s), ((it / kAStages) & 1) ^ 1)) { give_up(3); break; }
             const uint32_t a0_s = smem_s + kOffA + s * kAStage, a1_s = a0_s + kASub;
@@ -240,8 +260,8 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
                 const bool full_tile = nB == 64;
                 uint32_t m0r[16], m1r[16];
                 if (full_tile) load_man(mg, 0, m0r);
-                uint32_t stA = a.states[(size_t)t0 * 64 + lane], stB = a.states[(size_t)t0 * 64 + 32 + lane];
-                const uint32_t ml = a.tile_max_lens[t0];
+                uint32_t stA = cur.stA, stB = cur.stB;
+                const uint32_t ml = cur.ml;
                 if (!mbar_wait_warp(bar(kBarCopy + warp * 2 + cs), copy_parity[cs])) { give_up(4); break; }
                 copy_parity[cs] ^= 1;
                 const uint32_t win_s = copy_s + cs * p.win_cap;
@@ -311,6 +331,8 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
             fence_async_proxy();                                         // generic writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kBarFullA + s));
+            cur = nxt;
+            nxt = nxt2;
         }
     } else if (warp == kTmaWarp) {
         // =========================== TMA producer: activation tiles ================================
@@ -387,72 +409,50 @@ k_linear_gemm(const __grid_constant__ GemmArgs p, const __grid_constant__ CUtens
                 }
         }
     }
-    if (p.splits > 1) {
-        // deterministic split-K: the CTA that arrives last adds the partials in split order
-        uint32_t *ticket = a.tickets + (mtile * gridDim.x + nblk);
-        if (last_arrival(ticket, p.splits, s_flag)) {
-            // Four consecutive columns per thread, four rows per pass, all splits loaded before the first add:
-            // up to 32 independent 16-byte loads in flight per thread instead of one L2 round trip per term.
-            const bool vec = (g.N & 3u) == 0 && (a.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 7u) == 0;
-            const uint32_t quads = kBN / 4, items = m_here * quads;
-            for (uint32_t base = threadIdx.x; base < items; base += 4 * blockDim.x) {
-                float4 acc4[4];
-                float4 t[4][8];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint32_t idx = base + u * blockDim.x;
-                    const uint32_t m = m0 + idx / quads, n = nblk * kBN + (idx % quads) * 4;
-                    const bool in = idx < items && n < g.N;
-#pragma unroll
-                    for (int sidx = 0; sidx < 8; ++sidx) {
-                        t[u][sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (in && (uint32_t)sidx < p.splits) {
-                            const float *src = a.partial + ((size_t)sidx * a.M + m) * g.N + n;
-                            if (vec) t[u][sidx] = __ldcg(reinterpret_cast<const float4 *>(src));
-                            else {
-                                t[u][sidx].x = __ldcg(src);
-                                if (n + 1 < g.N) t[u][sidx].y = __ldcg(src + 1);
-                                if (n + 2 < g.N) t[u][sidx].z = __ldcg(src + 2);
-                                if (n + 3 < g.N) t[u][sidx].w = __ldcg(src + 3);
-                            }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    acc4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                    for (int sidx = 0; sidx < 8; ++sidx) {              // fixed split order
-                        acc4[u].x += t[u][sidx].x; acc4[u].y += t[u][sidx].y;
-                        acc4[u].z += t[u][sidx].z; acc4[u].w += t[u][sidx].w;
-                    }
-                    const uint32_t idx = base + u * blockDim.x;
-                    if (idx >= items) continue;
-                    const uint32_t m = m0 + idx / quads, n = nblk * kBN + (idx % quads) * 4;
-                    const float v[4] = {acc4[u].x, acc4[u].y, acc4[u].z, acc4[u].w};
-                    uint16_t o[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float f = v[e];
-                        if (a.bias && n + e < g.N) f += load_bf16(a.bias + n + e);
-                        o[e] = float_to_bf16_bits(f);
-                    }
-                    uint16_t *dst = a.y + (size_t)m * a.ldy + n;
-                    if (vec && n + 3 < g.N) {
-                        *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16));
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (n + e < g.N) dst[e] = o[e];
-                    }
-                }
-            }
-            if (threadIdx.x == 0) *ticket = 0;
-        }
-    }
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// Split-K epilogue: y = bf16(sum over splits of the fp32 partials (+ bias)), fixed summation order
+// (deterministic).  A separate grid over the whole chip: one CTA per output block would have to pull
+// splits x 256 KB through a single SM.  Launched with programmatic dependent launch right behind the GEMM.
+__global__ void __launch_bounds__(256) k_splitk_reduce(const float *__restrict__ partial, uint32_t splits, uint32_t M,
+                                                        uint32_t N, const uint16_t *__restrict__ bias, uint16_t *y,
+                                                        int64_t ldy, uint32_t vec) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t plane = (size_t)M * N;
+    if (vec) {
+        const uint32_t quads = N / 4;
+        const size_t items = (size_t)M * quads;
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < items; idx += (size_t)gridDim.x * blockDim.x) {
+            const uint32_t m = (uint32_t)(idx / quads), n = (uint32_t)(idx % quads) * 4;
+            const float *src = partial + (size_t)m * N + n;
+            float4 t[8];
+#pragma unroll
+            for (int sidx = 0; sidx < 8; ++sidx)                         // every split in flight before the first add
+                t[sidx] = (uint32_t)sidx < splits ? __ldcg(reinterpret_cast<const float4 *>(src + sidx * plane))
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 acc = t[0];
+#pragma unroll
+            for (int sidx = 1; sidx < 8; ++sidx) { acc.x += t[sidx].x; acc.y += t[sidx].y; acc.z += t[sidx].z; acc.w += t[sidx].w; }
+            if (bias) {
+                acc.x += load_bf16(bias + n); acc.y += load_bf16(bias + n + 1);
+                acc.z += load_bf16(bias + n + 2); acc.w += load_bf16(bias + n + 3);
+            }
+            const uint32_t lo = float_to_bf16_bits(acc.x) | ((uint32_t)float_to_bf16_bits(acc.y) << 16);
+            const uint32_t hi = float_to_bf16_bits(acc.z) | ((uint32_t)float_to_bf16_bits(acc.w) << 16);
+            *reinterpret_cast<uint2 *>(y + (size_t)m * ldy + n) = make_uint2(lo, hi);
+        }
+    } else {
+        for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < plane; idx += (size_t)gridDim.x * blockDim.x) {
+            const uint32_t m = (uint32_t)(idx / N), n = (uint32_t)(idx % N);
+            float acc = 0.f;
+            for (uint32_t sidx = 0; sidx < splits; ++sidx) acc += __ldcg(partial + sidx * plane + idx);
+            if (bias) acc += load_bf16(bias + n);
+            y[(size_t)m * ldy + n] = float_to_bf16_bits(acc);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------ host
@@ -515,7 +515,6 @@ int launch_linear_gemm(const LinArgs &a, uint32_t max_tile_len, size_t partial_c
     while (splits > 1 && (size_t)splits * a.M * g.N * sizeof(float) > partial_capacity) --splits;
     p.tiles_per_split = (g.tiles_k + splits - 1) / splits;
     p.splits = (g.tiles_k + p.tiles_per_split - 1) / p.tiles_per_split;
-    CI_REQUIRE(n_blocks * p.m_tiles < kTicketBytes - 1, "too many output blocks for the ticket area");
     p.status = a.tickets + (kTicketBytes - 1);
 
     CUtensorMap map;
@@ -535,9 +534,34 @@ int launch_linear_gemm(const LinArgs &a, uint32_t max_tile_len, size_t partial_c
         CI_CUDA(cudaFuncSetAttribute(k_linear_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         attr = true;
     }
-    dim3 grid(n_blocks, p.m_tiles, p.splits);
-    k_linear_gemm<<<grid, kGemmThreads, smem, s>>>(p, map);
-    CI_LAUNCH_CHECK(k_linear_gemm);
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(n_blocks, p.m_tiles, p.splits);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cfg.attrs = pdl;
+        cfg.numAttrs = 1;
+        CI_CUDA(cudaLaunchKernelEx(&cfg, k_linear_gemm, p, map));
+    }
+    if (p.splits > 1) {
+        const uint32_t vec = ((g.N & 3u) == 0 && (a.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(a.y) & 7u) == 0) ? 1u : 0u;
+        const size_t items = vec ? (size_t)a.M * (g.N / 4) : (size_t)a.M * g.N;
+        size_t blocks = (items + 255) / 256;
+        const size_t cap = (size_t)sm_count() * 16;
+        if (blocks > cap) blocks = cap;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cfg.attrs = pdl;
+        cfg.numAttrs = 1;
+        CI_CUDA(cudaLaunchKernelEx(&cfg, k_splitk_reduce, (const float *)a.partial, p.splits, a.M, g.N, a.bias, a.y,
+                                   a.ldy, vec));
+    }
     return CI_OK;
 }
 
