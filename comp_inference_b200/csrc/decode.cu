@@ -211,7 +211,9 @@ static int decode_tiled(const ci_tiled_weight *w, void *d_out, cudaStream_t s) {
     if (rc) return rc;
     CI_REQUIRE(d_out != nullptr, "null output");
     DecArgs a = make_args(w);
-    rc = launch_decode_staged(a, w->max_tile_len, BF16, d_out, s);   // staged path when the tensor qualifies
+    rc = launch_decode4(a, w->max_tile_len, BF16, d_out, s);         // 32-wide tiles, whole tile rows
+    if (rc <= 0) return rc;
+    rc = launch_decode_staged(a, w->max_tile_len, BF16, d_out, s);   // other staged shapes
     if (rc <= 0) return rc;
     uint32_t n_tasks = a.g.tiles_k * a.g.groups;
     size_t smem = kProbScale * 4 + (size_t)kDecWarps * kStageBytes;
