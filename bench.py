@@ -189,6 +189,31 @@ def secondary_metrics(mods, device):
     return out
 
 
+def kernels_once(args):
+    """One small invocation of each hot kernel on one 4096x4096 weight (24 MB compressed, nothing else resident):
+    the case the ncu captures summarised under profiles/ are taken on.  Prints parity figures, no timing."""
+    import comp_inference_b200 as ci
+    torch.cuda.set_device(0)
+    K = N = HIDDEN
+    W = make_weight_kn(K, N, 1001).cuda()
+    c = ci.compress_weight_cuda(W, TILE_H, TILE_W)
+    m = ci.RansLinear(K, N, c["tile_height"], c["tile_width"]).load_compressed(c).cuda()
+    g = torch.Generator().manual_seed(7)
+    x1 = torch.randn(1, K, generator=g).to(torch.bfloat16).cuda()
+    x512 = torch.randn(512, K, generator=g).to(torch.bfloat16).cuda()
+    for _ in range(3):
+        y1 = m(x1)                                                    # k_linear_mma4
+        y512 = m(x512)                                                # k_linear_gemm + k_splitk_reduce
+        w = ci.rans_decompress_bf16(m.rans_exp_stream, m.rans_exp_states, m.rans_exp_tables, m.rans_exp_slot_map,
+                                    (K, N), m.rans_exp_tile_offsets, m.rans_exp_tile_max_lens, m.tile_k, m.tile_n,
+                                    m.rans_man_raw)                   # k_decode4
+    torch.cuda.synchronize()
+    ref1, ref512 = x1.float() @ W.float(), x512.float() @ W.float()
+    print(json.dumps({"kernels_once": True, "decode_bit_exact": bool(torch.equal(w.view(torch.int16), W.view(torch.int16))),
+                      "gemv_rel_err": float((y1.float() - ref1).abs().max() / ref1.abs().max()),
+                      "gemm_rel_err": float((y512.float() - ref512).abs().max() / ref512.abs().max())}))
+
+
 def cpu_baseline_run(M, steps, warmup):
     """Decode + matmul of the same block with the CPU oracle on all host cores; returns (tok/s, ms/step, cores)."""
     from oracle import oracle as O
@@ -380,8 +405,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--kernels-once", action="store_true",
+                    help="run each hot kernel three times on one 4096x4096 weight and exit (the ncu capture case)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernels_once:
+        kernels_once(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -294,9 +294,17 @@ int launch_decode4(const DecArgs &a, uint32_t max_tile_len, bool bf16, void *out
     const uint32_t fixed = kLutBytes + kDec4BarBytes;
     const uint32_t warp_bytes = 2 * p.stage_bytes;
     if ((uint32_t)max_smem < fixed + 4 * warp_bytes) return 1;
-    uint32_t warps = ((uint32_t)max_smem - fixed) / warp_bytes;
-    if (warps > kDec4Warps) warps = kDec4Warps;
+    uint32_t w_max = ((uint32_t)max_smem - fixed) / warp_bytes;
+    if (w_max > kDec4Warps) w_max = kDec4Warps;
+    // A multiprocessor decodes at a fixed rate once it has about eight warps, so the run time follows the
+    // units per multiprocessor: pick the warp count that makes (rounds per warp) x (warps) smallest.
     const uint32_t P = (uint32_t)sm_count();
+    uint32_t warps = w_max;
+    uint64_t best = ~0ull;
+    for (uint32_t w = w_max < 8 ? w_max : 8; w <= w_max; ++w) {
+        const uint64_t rounds = (p.total + (uint64_t)P * w - 1) / ((uint64_t)P * w);
+        if (rounds * w <= best) { best = rounds * w; warps = w; }
+    }
     uint32_t blocks = (p.total + warps - 1) / warps;
     if (blocks > P) blocks = P;
     const size_t smem = fixed + (size_t)warps * warp_bytes;
