@@ -82,18 +82,52 @@ class RansLinear(_RansBase):
 
 
 class RansLMHead(_RansBase):
-    """LM head whose weight is stored [V=out, H=in] (pytorch_runtime.py:462-505)."""
+    """LM head whose weight is stored [V=out, H=in] (pytorch_runtime.py:462-505).
 
-    def __init__(self, in_features: int, out_features: int, tile_k: int = 1024, tile_n: int = 32):
+    The reference keeps the head in the embedding's layout so that a tied table is stored once, and
+    contracts along the columns of that layout with a kernel of its own.  On a 180 GB part the cheaper
+    trade is a second encoding: with ``fast_twin`` (default) the first forward decodes the table once,
+    re-encodes its transpose [H, V] on the GPU (bit-exact weights, +0.72 bytes per weight of device
+    memory) and every call then runs the ordinary fused decode-linear, which is several times faster
+    than the column-contracting kernel.  ``fast_twin=False`` keeps the reference's single-copy behaviour.
+    """
+
+    def __init__(self, in_features: int, out_features: int, tile_k: int = 1024, tile_n: int = 32,
+                 fast_twin: bool = True, twin_tile=(128, 32)):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.tile_k, self.tile_n = tile_k, tile_n
+        self.fast_twin, self.twin_tile = bool(fast_twin), (int(twin_tile[0]), int(twin_tile[1]))
         self._register()
+
+    _twin = None
+
+    def _twin_weight(self):
+        """Descriptor of the [H, V] re-encoding, built on first use and rebuilt if the buffers change."""
+        V, H = self.out_features, self.in_features
+        key = (self.rans_exp_stream.data_ptr(), self.rans_exp_states.data_ptr(), self.rans_man_raw.data_ptr())
+        if self._twin is None or self._twin[0] != key:
+            from . import comp_inference as ci_mod
+            w_vh = ops.rans_decompress_bf16(self.rans_exp_stream, self.rans_exp_states, self.rans_exp_tables,
+                                            self.rans_exp_slot_map, (V, H), self.rans_exp_tile_offsets,
+                                            self.rans_exp_tile_max_lens, int(self.tile_k), int(self.tile_n),
+                                            self.rans_man_raw)
+            c = ci_mod.compress_weight_cuda(w_vh.t().contiguous(), *self.twin_tile)
+            del w_vh
+            w, keep = _lib.tiled_weight(c["rans_exp_stream"], c["rans_exp_states"], c["rans_exp_tables"],
+                                        c["rans_exp_slot_map"], c["rans_exp_tile_offsets"],
+                                        c["rans_exp_tile_max_lens"], c["rans_man_raw"], H, V, int(c["tile_height"]),
+                                        int(c["tile_width"]), want_max=True)
+            self._twin = (key, w, keep, c)
+        return self._twin[1]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         V, H = self.out_features, self.in_features
         x2 = ops._check_x(x, H)
-        y = ops._linear_call(self._weight(V, H), x2, x2.shape[0], V, None, None, 0, True)
+        if self.fast_twin:
+            y = ops._linear_call(self._twin_weight(), x2, x2.shape[0], V, None, None, 0, False)
+        else:
+            y = ops._linear_call(self._weight(V, H), x2, x2.shape[0], V, None, None, 0, True)
         return y.view(*x.shape[:-1], V)
 
 

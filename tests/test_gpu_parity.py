@@ -266,6 +266,25 @@ def test_runtime_modules(ci, oracle):
     assert rel_err(head(xh).float().cpu().numpy(), refh) <= REL_TOL
 
 
+def test_lm_head_twin_and_single_copy_modes(ci):
+    """The head's re-encoded [H, V] twin holds the same weights bit for bit and both modes match a dense matmul."""
+    V, H = 1536, 512
+    W = make_weight(V, H, seed=77)
+    c = ci.compress_weight_cuda(W.cuda(), 128, 32)
+    twin = ci.RansLMHead(H, V, 128, 32).load_compressed(c)
+    single = ci.RansLMHead(H, V, 128, 32, fast_twin=False).load_compressed(c)
+    for M in (1, 3, 16):
+        x = torch.randn(M, H, generator=torch.Generator().manual_seed(5 + M)).to(torch.bfloat16).cuda()
+        ref = (x.double().cpu() @ W.double().t()).numpy()
+        assert rel_err(twin(x).float().cpu().numpy(), ref) <= REL_TOL
+        assert rel_err(single(x).float().cpu().numpy(), ref) <= REL_TOL
+    t = twin._twin[3]
+    back = ci.rans_decompress_bf16(t["rans_exp_stream"], t["rans_exp_states"], t["rans_exp_tables"],
+                                   t["rans_exp_slot_map"], (H, V), t["rans_exp_tile_offsets"],
+                                   t["rans_exp_tile_max_lens"], t["tile_height"], t["tile_width"], t["rans_man_raw"])
+    assert torch.equal(back.view(torch.uint16).cpu(), W.t().contiguous().view(torch.uint16))
+
+
 # ------------------------------------------------------------------ full benchmark sizes, by property
 
 @pytest.mark.parametrize("out_f,in_f,seed", [(4096, 4096, 1001), (11008, 4096, 1002), (4096, 11008, 1003)])
