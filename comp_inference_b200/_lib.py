@@ -73,6 +73,8 @@ SIGNATURES = {
                                   C.c_size_t, C.c_uint32, _S]),
     "ci_embedding_dense": (C.c_int, [C.POINTER(DenseWeight), _V, C.c_uint64, _V, C.c_int64, _S]),
     "ci_decode_legacy": (C.c_int, [_V, C.c_uint64, _V, _V, C.c_uint32, C.c_uint64, _V, _V, _V, _S]),
+    "ci_encode_legacy_sizes": (C.c_int, [_V, C.c_uint64, C.c_uint32, _V, _V, _V, _V, _S]),
+    "ci_encode_legacy_write": (C.c_int, [_V, C.c_uint64, C.c_uint32, _V, _V, _V, C.c_uint64, _S]),
 }
 
 _lib = None

@@ -152,6 +152,80 @@ class RansManager:
             num_tiles_n=tn, num_tiles_k=tk, tile_height=th, tile_width=tw)
 
 
+def _legacy_compress(self, data, freqs, cdf, min_block_size=512):
+    """RansManager.compress (src/python_bindings.cpp:225-299): legacy flat layout.  Accepts a numpy array or
+    a tensor (CPU or CUDA), returns CPU tensors like the reference.  Stream count as the reference chooses it
+    (src/cuda/rans_host.cuh:167-186): ceil(rows / min_block_size) * columns; symbol g + i * num_streams belongs
+    to stream g, the assignment its decoder inverts."""
+    import numpy as np
+    dev = _device()
+    t = torch.from_numpy(np.ascontiguousarray(data)) if isinstance(data, np.ndarray) else data
+    if t.dtype != torch.uint8:
+        raise RuntimeError("expected scalar type Byte")
+    rows = int(t.shape[0]) if t.dim() > 0 else 1
+    cols = int(t.shape[1]) if t.dim() > 1 else 1
+    n = t.numel()
+    if n == 0:
+        raise RuntimeError("empty input")
+    f = _as_u16_host(freqs, "freqs")
+    c = _as_u16_host(cdf, "cdf")
+    S = max(1, -(-rows // max(1, int(min_block_size))) * cols)
+    flat = t.to(dev).contiguous().view(-1)
+    states = torch.empty(S, dtype=torch.uint32, device=dev)
+    sizes = torch.empty(S, dtype=torch.uint32, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.ci_encode_legacy_sizes(_lib.ptr(flat), n, S, f.ctypes.data, c.ctypes.data, _lib.ptr(states),
+                                          _lib.ptr(sizes), _lib.stream()))
+    max_len = int(sizes.view(torch.int32).max().item())
+    stream = torch.empty(max_len * S, dtype=torch.uint8, device=dev)
+    _lib.check(lib.ci_encode_legacy_write(_lib.ptr(flat), n, S, f.ctypes.data, c.ctypes.data, _lib.ptr(stream),
+                                          stream.numel(), _lib.stream()))
+    tables, slot_map = _tables_host(f, c)
+    return TensorCompressResult(success=True, stream=stream.cpu(), states=states.cpu().view(torch.int32),
+                                sizes=sizes.cpu().view(torch.int32), tables=tables, slot_map=slot_map,
+                                checkpoints=torch.empty(0, dtype=torch.uint64), num_streams=S,
+                                stream_len=int(stream.numel()))
+
+
+def _legacy_decompress_into(self, stream, states, sizes, num_streams, freqs, cdf, output_buffer):
+    """RansManager.decompress_into (src/python_bindings.cpp:438-470): decodes into the caller's buffer
+    (numpy array or tensor, CPU or CUDA); returns the kernel time in milliseconds."""
+    import numpy as np
+    dev = _device()
+    as_t = lambda a: torch.from_numpy(np.ascontiguousarray(a)) if isinstance(a, np.ndarray) else a
+    f = _as_u16_host(freqs, "freqs")
+    c = _as_u16_host(cdf, "cdf")
+    tables, slot_map = _tables_host(f, c)
+    out_t = as_t(output_buffer) if not isinstance(output_buffer, np.ndarray) else torch.from_numpy(output_buffer)
+    d_out = out_t if out_t.is_cuda else torch.empty(out_t.numel(), dtype=torch.uint8, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    decompress(as_t(stream).to(dev), as_t(states).to(dev), as_t(sizes).to(dev), int(num_streams), tables.to(dev),
+               slot_map.to(dev), d_out.view(-1))
+    e1.record()
+    e1.synchronize()
+    if not out_t.is_cuda:
+        out_t.view(-1).copy_(d_out.cpu())
+    return e0.elapsed_time(e1)
+
+
+def _legacy_decompress(self, stream, states, sizes, num_streams, output_len, freqs, cdf):
+    """RansManager.decompress (src/python_bindings.cpp:399-436): returns (output, kernel ms); the output is a
+    numpy array for numpy input, else a uint8 tensor on the stream's device."""
+    import numpy as np
+    if isinstance(stream, np.ndarray):
+        out = np.empty(int(output_len), dtype=np.uint8)
+    else:
+        out = torch.empty(int(output_len), dtype=torch.uint8, device=stream.device)
+    ms = _legacy_decompress_into(self, stream, states, sizes, num_streams, freqs, cdf, out)
+    return out, ms
+
+
+RansManager.compress = _legacy_compress
+RansManager.decompress = _legacy_decompress
+RansManager.decompress_into = _legacy_decompress_into
+
+
 def decompress(stream, states, sizes, num_streams, tables, slot_map, output):
     """ccore.decompress (src/python_bindings.cpp:61-78): legacy flat layout, all CUDA tensors,
     writes into `output` on the current stream, does not synchronise."""

@@ -201,11 +201,73 @@ static int encode_write(const uint8_t *d_plane, uint32_t K, uint32_t N, const ui
     return CI_OK;
 }
 
+// Legacy flat layout, the inverse of k_decode_legacy: stream g holds the symbols at flat indices g,
+// g + num_streams, ... encoded last first; byte b of a stream is stored at stream + g + b * num_streams, so
+// the decoder, which starts at byte sizes[g] - 1, meets them in reverse order of emission.
+// stream == nullptr: count only.
+__global__ void __launch_bounds__(128) k_encode_legacy(const uint8_t *__restrict__ data, uint64_t n, uint32_t num_streams,
+                                                       const uint32_t *__restrict__ info, uint32_t *__restrict__ states,
+                                                       uint32_t *__restrict__ sizes, uint8_t *__restrict__ stream) {
+    __shared__ uint32_t s_info[256];
+    load_sym_info(s_info, info);
+    const uint32_t g = blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= num_streams) return;
+    const uint64_t per_stream = (n + num_streams - 1) / num_streams;
+    uint32_t state = kRansL, cnt = 0;
+    for (uint64_t i = per_stream; i-- > 0;) {
+        const uint64_t o = (uint64_t)g + i * num_streams;
+        if (o >= n) continue;
+        const uint32_t inf = s_info[data[o]];
+        const uint32_t freq = inf & 0xFFFFu, start = inf >> 16;
+        const uint32_t x_max = freq << 12;
+        while (state >= x_max) {
+            if (stream) stream[(size_t)g + (size_t)cnt * num_streams] = (uint8_t)(state & 0xFFu);
+            ++cnt;
+            state >>= 8;
+        }
+        const uint32_t q = state / freq;
+        state = (q << kProbBits) + (state - q * freq) + start;
+    }
+    if (states) states[g] = state;
+    if (sizes) sizes[g] = cnt;
+}
+
 }  // namespace ci
 
 using namespace ci;
 
 extern "C" {
+
+int ci_encode_legacy_sizes(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                           const uint16_t *cdf, uint32_t *d_states, uint32_t *d_sizes, ci_stream_t stream) {
+    CI_REQUIRE(d_data && d_states && d_sizes && freqs && cdf, "null pointer");
+    CI_REQUIRE(num_streams > 0 && n > 0, "empty input");
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t *d_info = nullptr;
+    int rc = upload_sym_info(freqs, cdf, &d_info, s);
+    if (rc) return rc;
+    k_encode_legacy<<<(num_streams + 127) / 128, 128, 0, s>>>(d_data, n, num_streams, d_info, d_states, d_sizes, nullptr);
+    CI_LAUNCH_CHECK(k_encode_legacy);
+    CI_CUDA(cudaFreeAsync(d_info, s));
+    return CI_OK;
+}
+
+int ci_encode_legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                           const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len, ci_stream_t stream) {
+    CI_REQUIRE(d_data && freqs && cdf, "null pointer");
+    CI_REQUIRE(d_stream || stream_len == 0, "null stream buffer");
+    CI_REQUIRE(num_streams > 0 && n > 0, "empty input");
+    if (stream_len == 0) return CI_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t *d_info = nullptr;
+    int rc = upload_sym_info(freqs, cdf, &d_info, s);
+    if (rc) return rc;
+    CI_CUDA(cudaMemsetAsync(d_stream, 0, stream_len, s));
+    k_encode_legacy<<<(num_streams + 127) / 128, 128, 0, s>>>(d_data, n, num_streams, d_info, nullptr, nullptr, d_stream);
+    CI_LAUNCH_CHECK(k_encode_legacy);
+    CI_CUDA(cudaFreeAsync(d_info, s));
+    return CI_OK;
+}
 
 int ci_encode_tiled_sizes(const uint8_t *d_plane, uint32_t K, uint32_t N, const uint16_t *freqs, const uint16_t *cdf,
                           uint32_t th, uint32_t tw, uint32_t *d_states, uint32_t *d_sizes, uint32_t *d_tile_offsets,

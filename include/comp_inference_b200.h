@@ -238,6 +238,18 @@ int ci_decode_legacy(const uint8_t *d_stream, uint64_t stream_len, const uint32_
                      uint32_t num_streams, uint64_t output_len, const uint32_t *d_tables, const uint8_t *d_slot_map,
                      uint8_t *d_out, ci_stream_t stream);
 
+/* Encoder of the same layout, two steps like the tiled encoder: _sizes writes the final state and byte count
+ * of every stream (the caller takes the maximum count, allocates max * num_streams bytes), _write stores byte b
+ * of stream g at d_stream[g + b * num_streams] (zero above a short stream).  num_streams as the reference chooses
+ * it: ceil(rows / min_block_size) * columns.  Replaces RansManager.compress
+ * (src/python_bindings.cpp:225-299 -> src/cuda/rans_ops.cu:17-72); the reference's own legacy encoder assigns
+ * symbols to streams by (row segment, column), which its decoder above does not invert, so this follows the
+ * decoder. */
+int ci_encode_legacy_sizes(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                           const uint16_t *cdf, uint32_t *d_states, uint32_t *d_sizes, ci_stream_t stream);
+int ci_encode_legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                           const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len, ci_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

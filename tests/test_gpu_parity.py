@@ -266,6 +266,33 @@ def test_runtime_modules(ci, oracle):
     assert rel_err(head(xh).float().cpu().numpy(), refh) <= REL_TOL
 
 
+@pytest.mark.parametrize("rows,cols,block", [(1024, 64, 512), (777, 33, 256), (100, 1, 512), (4096, 256, 512)])
+def test_legacy_flat_layout_round_trip(ci, rows, cols, block):
+    """RansManager.compress / decompress / decompress_into and ccore.decompress on the legacy flat layout."""
+    g = torch.Generator().manual_seed(rows + cols)
+    plane = torch.randint(100, 132, (rows, cols), generator=g, dtype=torch.int32).to(torch.uint8)
+    plane[0, 0] = 3                                             # a rare symbol: second renormalisation byte
+    freqs, cdf = ci.get_rans_lut(plane)
+    mgr = ci.ccore.RansManager(plane.numel())
+    r = mgr.compress(plane, freqs, cdf, block)
+    assert r.success and r.num_streams == -(-rows // block) * cols
+    assert r.stream.numel() == r.stream_len == int(r.sizes.max()) * r.num_streams
+    out, ms = mgr.decompress(r.stream.cuda(), r.states.cuda(), r.sizes.cuda(), r.num_streams, plane.numel(), freqs, cdf)
+    assert ms >= 0 and torch.equal(out.cpu().view(rows, cols), plane)
+    out_np, _ = mgr.decompress(r.stream.numpy(), r.states.numpy().view(np.uint32), r.sizes.numpy().view(np.uint32),
+                               r.num_streams, plane.numel(), freqs, cdf)
+    assert np.array_equal(out_np.reshape(rows, cols), plane.numpy())
+    buf = torch.zeros(plane.numel(), dtype=torch.uint8, device="cuda")
+    mgr.decompress_into(r.stream.cuda(), r.states.cuda(), r.sizes.cuda(), r.num_streams, freqs, cdf, buf)
+    assert torch.equal(buf.cpu().view(rows, cols), plane)
+    buf2 = torch.zeros(plane.numel(), dtype=torch.uint8, device="cuda")
+    ci.ccore.decompress(r.stream.cuda(), r.states.cuda(), r.sizes.cuda(), r.num_streams, r.tables.cuda(),
+                        r.slot_map.cuda(), buf2)
+    assert torch.equal(buf2, buf)
+    r2 = mgr.compress(plane.numpy(), freqs, cdf, block)         # numpy overload
+    assert torch.equal(r2.stream, r.stream) and torch.equal(r2.states, r.states)
+
+
 def test_lm_head_twin_and_single_copy_modes(ci):
     """The head's re-encoded [H, V] twin holds the same weights bit for bit and both modes match a dense matmul."""
     V, H = 1536, 512
