@@ -44,9 +44,9 @@ LAYERS = [("q_proj", HIDDEN, HIDDEN, 1001, "col"), ("k_proj", HIDDEN, HIDDEN, 10
           ("down_proj", FFN, HIDDEN, 1003, "row")]
 METRIC = "fused decode-GEMV tok/s (one Llama-2-7B decoder block: 7 rANS-compressed linears)"
 # DRAM bytes (read + write) per launch of the fused kernel from one ncu capture of the 4096x4096 layer
-# (profiles/linear_mma_4096x4096_tile128.md); traffic grows with the compressed size, so a step's
+# (profiles/linear_mma4_4096x4096_tile128.md); traffic grows with the compressed size, so a step's
 # average launch is scaled by its compressed bytes.
-NCU_TRAFFIC_4096 = 24.16e6
+NCU_TRAFFIC_4096 = 24.15e6
 NCU_BYTES_4096 = 24.06e6
 
 
@@ -186,6 +186,22 @@ def secondary_metrics(mods, device):
     flops = sum(2.0 * 512 * m.in_features * m.out_features for m in mods.values())
     out["prefill_M512"] = {"tok_s": 512 / (ms * 1e-3), "ms_per_block": ms, "TFLOPs": flops / (ms * 1e-3) / 1e12,
                            "kernel": "k_linear_gemm (tcgen05.mma, TMEM accumulators)"}
+    # vocabulary table 32000 x 4096 stored [V, H]: row gather of 4096 ids, and the LM head at batch 1
+    V = 32000
+    table = make_weight_kn(V, HIDDEN, 1004).to(device)
+    c = ci.compress_weight_cuda(table, TILE_H, TILE_W)
+    emb = ci.RansEmbedding(V, HIDDEN, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
+    head = ci.RansLMHead(HIDDEN, V, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
+    ids = torch.randint(0, V, (4096,), generator=torch.Generator().manual_seed(3001)).to(device)
+    rows = emb(ids)
+    exact = bool(torch.equal(rows.view(torch.int16), table[ids].view(torch.int16)))
+    ms = timed(lambda: emb(ids), 10)
+    out["embedding_4096_ids"] = {"ms": ms, "out_GBs": 4096 * HIDDEN * 2 / (ms * 1e-3) / 1e9, "bit_exact": exact,
+                                 "symbols_decoded_per_emitted": (TILE_H // 2 + 1) / 2.0}
+    x1 = torch.randn(1, HIDDEN, generator=torch.Generator().manual_seed(2001)).to(torch.bfloat16).to(device)
+    head(x1)                                                       # builds the transposed twin
+    ms = timed(lambda: head(x1), 10)
+    out["lm_head_batch1"] = {"ms": ms, "effective_uncompressed_GBs": 2.0 * V * HIDDEN / (ms * 1e-3) / 1e9}
     return out
 
 

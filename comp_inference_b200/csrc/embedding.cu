@@ -5,20 +5,9 @@
 // columns) opens the row's half-tile streams and discards the symbols of the rows
 // above it.  Only the bytes those skipped rows consume are touched, straight from
 // L2/global memory; ids outside [0,K) produce a zero row (embedding_triton.py:203-210).
-#include "common.cuh"
+#include "embedding.cuh"
 
 namespace ci {
-
-struct EmbArgs {
-    const uint8_t *stream;
-    const uint32_t *states, *tables, *tile_offsets, *tile_max_lens, *lut;
-    const uint8_t *slot_map, *mantissa;
-    Geom g;
-    const int64_t *ids;
-    uint64_t n_ids;
-    uint16_t *out;
-    int64_t ldo;
-};
 
 constexpr int kEmbWarps = 8;
 
@@ -133,6 +122,8 @@ int ci_embedding(const ci_tiled_weight *w, const int64_t *d_ids, uint64_t n_ids,
     a.tile_max_lens = w->tile_max_lens; a.lut = w->lut; a.slot_map = w->slot_map; a.mantissa = w->mantissa;
     a.g = make_geom(w->K, w->N, w->tile_h, w->tile_w);
     a.ids = d_ids; a.n_ids = n_ids; a.out = d_out; a.ldo = ldo;
+    rc = launch_embedding4(a, w->max_tile_len, (cudaStream_t)stream);  // 32-wide tiles: four streams per lane
+    if (rc <= 0) return rc;
     uint64_t tasks = n_ids * a.g.groups, blocks = (tasks + kEmbWarps - 1) / kEmbWarps, cap = (uint64_t)sm_count() * 8;
     if (blocks > cap) blocks = cap;
     k_embedding<<<(uint32_t)blocks, kEmbWarps * 32, 0, (cudaStream_t)stream>>>(a);

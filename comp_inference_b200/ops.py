@@ -116,7 +116,7 @@ def fused_rans_embedding_triton(x, compressed_data, initial_states, tables, slot
     ids = x.reshape(-1).to(torch.int64).contiguous()
     n = ids.numel()
     w, keep = _lib.tiled_weight(compressed_data, initial_states, tables, slot_map, tile_offsets, tile_max_lens,
-                                mantissas, K, N, int(tile_k), int(tile_n))
+                                mantissas, K, N, int(tile_k), int(tile_n), want_max=True)
     o = out.view(n, N) if out is not None else torch.empty((n, N), device=x.device, dtype=torch.bfloat16)
     if o.dtype != torch.bfloat16 or (n > 0 and o.stride(1) != 1):
         raise RuntimeError("out must be a bfloat16 tensor with unit inner stride")
