@@ -77,6 +77,10 @@ SHAPES = [
     (96, 64, 64, 32), (100, 70, 32, 16), (256, 128, 1024, 32), (48, 33, 16, 32), (16, 8, 16, 8),
     (130, 200, 64, 64), (64, 256, 32, 128), (1000, 96, 128, 32), (33, 5, 16, 8), (2048, 512, 1024, 32),
     (512, 1024, 128, 32), (300, 100, 256, 16),
+    # whole tile rows of 32-wide tiles: the four-streams-per-lane kernels (tile heights 16..128, partial and
+    # single column tiles, an odd number of tile rows, N not a multiple of 4)
+    (256, 96, 16, 32), (384, 160, 32, 32), (512, 100, 64, 32), (256, 36, 128, 32), (768, 32, 128, 32),
+    (384, 64, 128, 32), (256, 70, 64, 32),
 ]
 
 
@@ -155,6 +159,7 @@ def test_fused_linear_bias_out_and_leading_dims(ci, oracle):
 
 
 @pytest.mark.parametrize("V,H,th,tw", [(96, 64, 64, 32), (1000, 256, 128, 32), (300, 96, 32, 16), (520, 128, 256, 64),
+                                       (640, 102, 128, 32), (200, 36, 16, 32), (512, 288, 64, 32),
                                         (2100, 64, 1024, 32)])
 @pytest.mark.parametrize("M", [1, 5])
 def test_transposed_linear_matches_oracle(ci, oracle, V, H, th, tw, M):
