@@ -186,6 +186,16 @@ def secondary_metrics(mods, device):
     flops = sum(2.0 * 512 * m.in_features * m.out_features for m in mods.values())
     out["prefill_M512"] = {"tok_s": 512 / (ms * 1e-3), "ms_per_block": ms, "TFLOPs": flops / (ms * 1e-3) / 1e12,
                            "kernel": "k_linear_gemm (tcgen05.mma, TMEM accumulators)"}
+    # the same 512 rows through the reference's other prefill route: stand-alone decode into a scratch buffer,
+    # then a library GEMM (RansLinear(prefill_policy="decode_then_gemm"))
+    for m in mods.values():
+        m.prefill_policy = "decode_then_gemm"
+    ms = timed(lambda: block_step(mods, x, 1), 10)
+    for m in mods.values():
+        m.prefill_policy = "fused"
+    out["prefill_M512_decode_then_gemm"] = {"tok_s": 512 / (ms * 1e-3), "ms_per_block": ms,
+                                            "TFLOPs": flops / (ms * 1e-3) / 1e12,
+                                            "kernel": "k_decode4 into an L2-sized scratch + cuBLAS bf16 GEMM"}
     # vocabulary table 32000 x 4096 stored [V, H]: row gather of 4096 ids, and the LM head at batch 1
     V = 32000
     table = make_weight_kn(V, HIDDEN, 1004).to(device)

@@ -58,6 +58,9 @@ __global__ void __launch_bounds__(512, 1) k_decode_staged(const __grid_constant_
     if (gw < p.total) issue(gw, 0);
     load_lut(s_lut, a.lut, a.tables, a.slot_map);
     __syncthreads();
+    // Programmatic dependent launch: the output may still be in use by the previous kernel of the stream.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const uint32_t lut_s = smem_s;
     uint32_t parity0 = 0, parity1 = 0, stage = 0;
@@ -152,8 +155,17 @@ static int launch_tw(const StagedDecArgs &p, uint32_t blocks, uint32_t warps, si
         CI_CUDA(cudaFuncSetAttribute(k_decode_staged<TW, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         attr = true;
     }
-    k_decode_staged<TW, BF16><<<blocks, warps * 32, smem, s>>>(p, out);
-    CI_LAUNCH_CHECK(k_decode_staged);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    CI_CUDA(cudaLaunchKernelEx(&cfg, k_decode_staged<TW, BF16>, p, out));
     return CI_OK;
 }
 

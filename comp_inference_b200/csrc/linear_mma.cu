@@ -138,6 +138,11 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
     if (lo < hi) issue(lo, 0, nx_begin, nx_end);
     load_lut(s_lut, a.lut, a.tables, a.slot_map);
     __syncthreads();
+    // Only the weight was read so far.  Under programmatic dependent launch the activations, the workspace
+    // and the output may still belong to the previous kernel of the stream: wait for it, then let the next
+    // launch start its preamble (no-ops in an ordinary launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (lo >= hi) return;                                       // no CTA-wide synchronisation below this line
 
     float acc[4][4];
@@ -429,8 +434,17 @@ static int launch_tw(const MmaArgs &p, uint32_t blocks, uint32_t warps, size_t s
         CI_CUDA(cudaFuncSetAttribute(k_linear_mma<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         attr = true;
     }
-    k_linear_mma<TW><<<blocks, warps * 32, smem, s>>>(p);
-    CI_LAUNCH_CHECK(k_linear_mma);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    CI_CUDA(cudaLaunchKernelEx(&cfg, k_linear_mma<TW>, p));
     return CI_OK;
 }
 

@@ -461,6 +461,11 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     const uint32_t P = (uint32_t)sm_count();
     p.pairs_k = g.tiles_k / 2;
     p.total = g.groups * p.pairs_k;
+    // A unit here is a serial chain twice as long as in the two-streams kernel (two tiles instead of one).
+    // That pays once the multiprocessors are saturated (about eight warps each); a small matrix -- a
+    // tensor-parallel shard, say -- is latency bound and finishes sooner with the shorter units
+    // (measured cross-over: 4096 x 2048 at tile height 128).
+    if (p.total < P * 6) return 1;
     uint32_t best_w = w_max;
     double best = -1.0;
     for (uint32_t w = 4; w <= w_max; ++w) {

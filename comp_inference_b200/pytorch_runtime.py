@@ -59,14 +59,37 @@ class _RansBase(nn.Module):
         return self._handle[1]
 
 
+_scratch = {}
+
+
+def _decode_scratch(device, K, N):
+    """One bf16 buffer per device, grown on demand, that the decode-then-GEMM prefill path decodes into."""
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < K * N:
+        buf = torch.empty(K * N, dtype=torch.bfloat16, device=device)
+        _scratch[device] = buf
+    return buf[:K * N].view(K, N)
+
+
 class RansLinear(_RansBase):
-    """nn.Linear replacement; weight stored compressed as [K=in, N=out] (pytorch_runtime.py:397-459)."""
+    """nn.Linear replacement; weight stored compressed as [K=in, N=out] (pytorch_runtime.py:397-459).
+
+    ``prefill_policy`` chooses what a call with many activation rows runs:
+    "fused" (default) the decode-GEMM kernel (tcgen05, the decoded weight never leaves the chip);
+    "decode_then_gemm" the stand-alone decoder into a reused per-device scratch buffer followed by a
+    library GEMM -- the reference's decompress + triton_matmul pair (comp_inference/triton_gemm.py:324-337) --
+    which at present is the faster of the two from ``prefill_rows`` rows up because the decoder runs at
+    twice the rate of the GEMM's decode warps and the weight is decoded once however many rows there are.
+    """
 
     def __init__(self, in_features: int, out_features: int, tile_k: int = 1024, tile_n: int = 32, split_k: int = 1,
-                 has_bias: bool = False):
+                 has_bias: bool = False, prefill_policy: str = "fused", prefill_rows: int = 256):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.tile_k, self.tile_n, self.split_k = tile_k, tile_n, split_k
+        if prefill_policy not in ("fused", "decode_then_gemm"):
+            raise ValueError("prefill_policy must be 'fused' or 'decode_then_gemm'")
+        self.prefill_policy, self.prefill_rows = prefill_policy, int(prefill_rows)
         self._register()
         if has_bias:
             self.register_buffer("bias", torch.empty(out_features, dtype=torch.bfloat16))
@@ -76,6 +99,13 @@ class RansLinear(_RansBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         K, N = self.in_features, self.out_features
         x2 = ops._check_x(x, K)
+        if self.prefill_policy == "decode_then_gemm" and x2.shape[0] >= self.prefill_rows:
+            w = _decode_scratch(x2.device, K, N)
+            _lib.check(_lib.load().ci_decode_bf16(self._weight(K, N), _lib.ptr(w), _lib.stream()))
+            y = torch.matmul(x2, w)
+            if self.bias is not None:
+                y += self.bias
+            return y.view(*x.shape[:-1], N)
         y = ops._linear_call(self._weight(K, N), x2, x2.shape[0], N, self.bias, None,
                              self.split_k if self.split_k > 1 else 0, False)
         return y.view(*x.shape[:-1], N)

@@ -298,6 +298,23 @@ def test_legacy_flat_layout_round_trip(ci, rows, cols, block):
     assert torch.equal(r2.stream, r.stream) and torch.equal(r2.states, r.states)
 
 
+def test_prefill_policies_agree(ci):
+    """RansLinear's two prefill routes (fused decode-GEMM, decode + library GEMM) against a dense matmul."""
+    K, N, M = 512, 384, 300
+    W = make_weight(K, N, seed=91)
+    c = ci.compress_weight_cuda(W.cuda(), 128, 32)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).cuda()
+    ref = (x.double().cpu() @ W.double() + bias.double().cpu()).numpy()
+    for policy in ("fused", "decode_then_gemm"):
+        lin = ci.RansLinear(K, N, 128, 32, has_bias=True, prefill_policy=policy).load_compressed(c).cuda()
+        lin.bias = bias
+        assert rel_err(lin(x).float().cpu().numpy(), ref) <= REL_TOL, policy
+        assert rel_err(lin(x[:3]).float().cpu().numpy(), ref[:3]) <= REL_TOL, policy      # few rows: always fused
+    with pytest.raises(ValueError):
+        ci.RansLinear(K, N, 128, 32, prefill_policy="other")
+
+
 def test_lm_head_twin_and_single_copy_modes(ci):
     """The head's re-encoded [H, V] twin holds the same weights bit for bit and both modes match a dense matmul."""
     V, H = 1536, 512
