@@ -38,8 +38,10 @@ from .pytorch_runtime import (  # noqa: F401
     RansEmbedding,
     RansLinear,
     RansLMHead,
+    RansRowParallelLinear,
     RansWorkspace,
     load_compressed_model_with_auto_model,
+    patch_model_tensor_parallel,
 )
 
 __all__ = [n for n in dir() if not n.startswith("_")]

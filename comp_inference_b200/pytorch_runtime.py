@@ -227,3 +227,110 @@ def load_compressed_model_with_auto_model(model_id: str, safetensors_path: str, 
     patch_model(model, state_dict, quant.get("layer_configs", {}), quant.get("default_tile_height", 1024),
                 quant.get("default_tile_width", 32), split_k)
     return model.cuda()
+
+
+# ------------------------------------------------------------------------- tensor parallel
+
+_COLUMN_PARALLEL = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")
+_ROW_PARALLEL = ("o_proj", "down_proj")
+
+
+class RansRowParallelLinear(RansLinear):
+    """Row shard (a slice of the input features) of a compressed linear: every rank multiplies its
+    slice and the partial outputs are summed over the group -- the only exchange of a tensor-parallel
+    block, on activations; compressed weights never move.  The bias is added once, after the sum."""
+
+    def __init__(self, *args, group=None, **kw):
+        super().__init__(*args, **kw)
+        self.group = group
+
+    def forward(self, x):
+        import torch.distributed as dist
+        bias, self.bias = self.bias, None
+        try:
+            y = super().forward(x)
+        finally:
+            self.bias = bias
+        dist.all_reduce(y, group=self.group)
+        if bias is not None:
+            y += bias
+        return y
+
+
+def _state_to_compressed(state_dict, name, th, tw):
+    """The package tensors of one module as the dict sharding.shard_rows / shard_cols work on."""
+    info = state_dict[name + ".rans_info"].tolist()
+    rank = info[6]
+    shape = tuple(info[11:11 + rank]) if len(info) >= 11 + rank else None
+    c = {k: state_dict[f"{name}.{k}"] for k in ("rans_exp_stream", "rans_exp_states", "rans_exp_tables",
+                                                "rans_exp_slot_map", "rans_exp_tile_offsets",
+                                                "rans_exp_tile_max_lens", "rans_man_raw")}
+    if len(info) >= 11 and info[9] and info[10]:
+        th, tw = int(info[9]), int(info[10])
+    c.update(shape=(int(shape[0]), int(shape[1])), tile_height=int(th), tile_width=int(tw))
+    return c
+
+
+def _shard(c, kind, rank, world, device):
+    """This rank's shard of a compressed [K, N] weight.  Cut out of the compressed arrays when the cut falls
+    on tile boundaries; otherwise (Llama-2's 11008 rows over 8 ranks = 10.75 tiles) the rank decodes the
+    weight once on the GPU and re-encodes its slice."""
+    from . import sharding
+    from . import comp_inference as ci_mod
+    K, N = c["shape"]
+    th, tw = c["tile_height"], c["tile_width"]
+    if kind == "col" and sharding.can_shard_cols(N, tw, world):
+        return sharding.shard_cols(c, rank, world)
+    if kind == "row" and sharding.can_shard_rows(K, th, world):
+        return sharding.shard_rows(c, rank, world)
+    if (kind == "col" and N % world) or (kind == "row" and K % world):
+        raise ValueError(f"{K}x{N} cannot be split {kind}-wise over {world} ranks")
+    g = {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = ops.rans_decompress_bf16(g["rans_exp_stream"], g["rans_exp_states"], g["rans_exp_tables"],
+                                 g["rans_exp_slot_map"], (K, N), g["rans_exp_tile_offsets"],
+                                 g["rans_exp_tile_max_lens"], th, tw, g["rans_man_raw"])
+    if kind == "col":
+        n = N // world
+        part = w[:, rank * n:(rank + 1) * n]
+    else:
+        k = K // world
+        part = w[rank * k:(rank + 1) * k]
+    return ci_mod.compress_weight_cuda(part.contiguous(), th, tw)
+
+
+def patch_model_tensor_parallel(model, state_dict, rank, world, group=None, layer_configs=None, default_th=1024,
+                                default_tw=32, device=None):
+    """patch_model for one rank of a tensor-parallel group.  q/k/v/gate/up projections are cut column-wise
+    (each rank owns a slice of the heads / of the FFN width), o/down projections row-wise with an all-reduce
+    of their outputs; embedding, LM head and every uncompressed parameter are replicated.  The attention
+    and MLP modules of the model are left as they are: they take the number of heads and the FFN width
+    from the tensors they are handed.  Returns the model, moved to ``device``."""
+    layer_configs = layer_configs or {}
+    device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    sharded = {}
+    for name, module in list(model.named_modules()):
+        if not isinstance(module, nn.Linear) or f"{name}.rans_exp_stream" not in state_dict:
+            continue
+        leaf = name.rsplit(".", 1)[-1]
+        kind = "col" if leaf in _COLUMN_PARALLEL else "row" if leaf in _ROW_PARALLEL else None
+        if kind is None or world == 1:
+            continue
+        th = layer_configs.get(name, {}).get("tile_height", default_th)
+        tw = layer_configs.get(name, {}).get("tile_width", default_tw)
+        c = _shard(_state_to_compressed(state_dict, name, th, tw), kind, rank, world, device)
+        k, n = c["shape"]
+        has_bias = module.bias is not None
+        if kind == "row":
+            new = RansRowParallelLinear(k, n, c["tile_height"], c["tile_width"], 1, has_bias, group=group)
+        else:
+            new = RansLinear(k, n, c["tile_height"], c["tile_width"], 1, has_bias)
+        new.load_compressed(c)
+        if has_bias:
+            b = state_dict[name + ".bias"].to(torch.bfloat16)
+            new.bias = b[rank * n:(rank + 1) * n].contiguous() if kind == "col" else b.contiguous()
+        parent_name, _, child = name.rpartition(".")
+        setattr(model.get_submodule(parent_name) if parent_name else model, child, new)
+        sharded[name] = new
+    rest = {k: v for k, v in state_dict.items() if not any(k.startswith(n + ".") for n in sharded)}
+    patch_model(model, rest, layer_configs, default_th, default_tw)
+    return model.to(device)

@@ -62,3 +62,38 @@ def test_package_round_trip_and_logits(tmp_path):
         a = loaded.generate(ids[:1].cuda(), max_new_tokens=8, do_sample=False)
         b = dense.generate(ids[:1].cuda(), max_new_tokens=8, do_sample=False)
     assert a.shape == b.shape
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_logits(tmp_path):
+    """Two ranks, each holding its column / row shards of every projection (cut out of the package's
+    compressed arrays), reproduce the single-GPU logits; only activations cross NCCL."""
+    import socket
+    import subprocess
+    import sys
+    import comp_inference_b200 as ci
+    cfg, model = tiny_llama()
+    ci.compress_model(model, tile_height=64, tile_width=32)
+    out_dir = ci.save_rans_model_package(model, None, str(tmp_path / "pkg"), fuse=False)
+    single = ci.load_compressed_model(out_dir).eval()
+    ids = torch.randint(0, cfg.vocab_size, (2, 16), generator=torch.Generator().manual_seed(4001))
+    with torch.no_grad():
+        logits = single(ids.cuda()).logits.float().cpu()
+    ref_path = str(tmp_path / "ref.pt")
+    torch.save({"ids": ids, "logits": logits}, ref_path)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = str(s.getsockname()[1])
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tp_worker.py")
+    procs = [subprocess.Popen([sys.executable, worker, out_dir, ref_path, str(r), "2", port],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n[timed out]"
+        outs.append(out)
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
