@@ -32,7 +32,8 @@
 namespace ci {
 
 constexpr uint32_t kBar4Bytes = 256;         // up to 16 warps x 2 stages x 8 B
-constexpr uint32_t kMma4Warps = 16;          // 512 threads x 128 registers
+constexpr uint32_t kMma4Warps = 14;          // 448 threads x 128 registers; an instantiation for 12 warps with 158
+                                             // registers executes 7 % fewer instructions but was slower (fewer warps)
 
 struct Mma4Args {
     LinArgs a;
