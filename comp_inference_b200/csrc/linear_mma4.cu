@@ -74,6 +74,58 @@ __device__ __forceinline__ uint32_t ldg_stream_u32(const void *src) {
     return v;
 }
 
+// Renormalisation of a lane's four streams.  The first byte (about one symbol in three needs it) is merged
+// under a predicate; a second byte is needed only after a symbol of frequency below 16, so the whole
+// warp tests for it with one vote and skips those instructions otherwise.
+__device__ __forceinline__ void renorm4(uint32_t &s0, uint32_t &s1, uint32_t &s2, uint32_t &s3, uint32_t &p0, uint32_t &p1,
+                                        uint32_t &p2, uint32_t &p3, uint32_t y0, uint32_t y1, uint32_t y2, uint32_t y3) {
+    const uint32_t lowest = min(min(s0, s1), min(s2, s3));
+    renorm_first<128>(s0, p0, y0);
+    renorm_first<128>(s1, p1, y1);
+    renorm_first<128>(s2, p2, y2);
+    renorm_first<128>(s3, p3, y3);
+    if (__any_sync(kFull, lowest < 256u)) {
+        renorm_fast<128>(s0, p0);
+        renorm_fast<128>(s1, p1);
+        renorm_fast<128>(s2, p2);
+        renorm_fast<128>(s3, p3);
+    }
+}
+
+// Four symbols of each of the lane's streams -> four B fragments -> four mma.  m = sign+mantissa words of
+// the four rows, xf = the activations of those rows (A fragment).
+__device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_t &s1, uint32_t &s2, uint32_t &s3,
+                                       uint32_t &p0, uint32_t &p1, uint32_t &p2, uint32_t &p3, uint32_t lut_s,
+                                       const uint32_t (&m)[4], const uint32_t (&xf)[4]) {
+    uint32_t b[4][2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {                               // two rows -> one packed pair per column
+        uint32_t y0 = lds_u8(p0), y1 = lds_u8(p1), y2 = lds_u8(p2), y3 = lds_u8(p3);
+        const uint32_t e0 = decode_fast(s0, lut_s);
+        const uint32_t e1 = decode_fast(s1, lut_s);
+        const uint32_t e2 = decode_fast(s2, lut_s);
+        const uint32_t e3 = decode_fast(s3, lut_s);
+        renorm4(s0, s1, s2, s3, p0, p1, p2, p3, y0, y1, y2, y3);
+        y0 = lds_u8(p0);
+        y1 = lds_u8(p1);
+        y2 = lds_u8(p2);
+        y3 = lds_u8(p3);
+        const uint32_t f0 = decode_fast(s0, lut_s);
+        const uint32_t f1 = decode_fast(s1, lut_s);
+        const uint32_t f2 = decode_fast(s2, lut_s);
+        const uint32_t f3 = decode_fast(s3, lut_s);
+        renorm4(s0, s1, s2, s3, p0, p1, p2, p3, y0, y1, y2, y3);
+        b[0][h] = weight_pair4<0>(e0, f0, m[2 * h], m[2 * h + 1]);
+        b[1][h] = weight_pair4<1>(e1, f1, m[2 * h], m[2 * h + 1]);
+        b[2][h] = weight_pair4<2>(e2, f2, m[2 * h], m[2 * h + 1]);
+        b[3][h] = weight_pair4<3>(e3, f3, m[2 * h], m[2 * h + 1]);
+    }
+    mma_bf16(acc[0], xf, b[0][0], b[0][1]);
+    mma_bf16(acc[1], xf, b[1][0], b[1][1]);
+    mma_bf16(acc[2], xf, b[2][0], b[2][1]);
+    mma_bf16(acc[3], xf, b[3][0], b[3][1]);
+}
+
 __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid_constant__ Mma4Args p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs &a = p.a;
@@ -299,51 +351,6 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
     uint32_t s0, s1, s2, s3, pos0, pos1, pos2, pos3;
     // Four symbols of each of the lane's streams -> four B fragments -> four mma.  m = sign+mantissa words
     // of the four rows, xf = the activations of those rows.
-    // Renormalisation of the four streams.  The first byte (about one symbol in three needs it) is merged
-    // under a predicate; a second byte is needed only after a symbol of frequency below 16, so the whole
-    // warp tests for it with one vote and skips those instructions otherwise.
-    auto renorm4 = [&](uint32_t y0, uint32_t y1, uint32_t y2, uint32_t y3) {
-        const uint32_t lowest = min(min(s0, s1), min(s2, s3));
-        renorm_first<128>(s0, pos0, y0);
-        renorm_first<128>(s1, pos1, y1);
-        renorm_first<128>(s2, pos2, y2);
-        renorm_first<128>(s3, pos3, y3);
-        if (__any_sync(kFull, lowest < 256u)) {
-            renorm_fast<128>(s0, pos0);
-            renorm_fast<128>(s1, pos1);
-            renorm_fast<128>(s2, pos2);
-            renorm_fast<128>(s3, pos3);
-        }
-    };
-    auto group = [&](const uint32_t (&m)[4], const uint32_t (&xf)[4]) {
-        uint32_t b[4][2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {                           // two rows -> one packed pair per column
-            uint32_t y0 = lds_u8(pos0), y1 = lds_u8(pos1), y2 = lds_u8(pos2), y3 = lds_u8(pos3);
-            const uint32_t e0 = decode_fast(s0, lut_s);
-            const uint32_t e1 = decode_fast(s1, lut_s);
-            const uint32_t e2 = decode_fast(s2, lut_s);
-            const uint32_t e3 = decode_fast(s3, lut_s);
-            renorm4(y0, y1, y2, y3);
-            y0 = lds_u8(pos0);
-            y1 = lds_u8(pos1);
-            y2 = lds_u8(pos2);
-            y3 = lds_u8(pos3);
-            const uint32_t f0 = decode_fast(s0, lut_s);
-            const uint32_t f1 = decode_fast(s1, lut_s);
-            const uint32_t f2 = decode_fast(s2, lut_s);
-            const uint32_t f3 = decode_fast(s3, lut_s);
-            renorm4(y0, y1, y2, y3);
-            b[0][h] = weight_pair4<0>(e0, f0, m[2 * h], m[2 * h + 1]);
-            b[1][h] = weight_pair4<1>(e1, f1, m[2 * h], m[2 * h + 1]);
-            b[2][h] = weight_pair4<2>(e2, f2, m[2 * h], m[2 * h + 1]);
-            b[3][h] = weight_pair4<3>(e3, f3, m[2 * h], m[2 * h + 1]);
-        }
-        mma_bf16(acc[0], xf, b[0][0], b[0][1]);
-        mma_bf16(acc[1], xf, b[1][0], b[1][1]);
-        mma_bf16(acc[2], xf, b[2][0], b[2][1]);
-        mma_bf16(acc[3], xf, b[3][0], b[3][1]);
-    };
     // Operands of one group straight from global memory: four 32-byte-strided words of the sign+mantissa
     // plane and two 8-byte quads of activations.
     auto fetch = [&](const uint8_t *mp, const uint16_t *xp0, const uint16_t *xp1, uint32_t (&m)[4], uint32_t (&xf)[4]) {
@@ -419,12 +426,12 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 #pragma unroll 1
         for (uint32_t gi = 0; gi < n_groups; gi += 2) {         // operands are fetched one group ahead
             fetch(mp + 128, xp0 + 4, xp1 + 4, mB, xB);
-            group(mA, xA);
+            group4(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
             mp += 256;
             xp0 += 8;
             xp1 += 8;
             if (gi + 2 < n_groups) fetch(mp, xp0, xp1, mA, xA);
-            group(mB, xB);
+            group4(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
         }
         stage ^= 1;
     }
