@@ -14,9 +14,9 @@ from pinned memory, the seven module calls and the copy of the result back to pi
 captured once with torch.cuda.graph and replayed, the host waiting for the result after every step.
 
 With --gpus N > 1 (launched under torch.distributed.run) the block is tensor parallel: q/k/v/gate/up
-are column shards, o/down row shards cut out of the compressed arrays, with an NCCL all-reduce on the
-activations after o and down; every rank decodes only its own shard.  Total work is fixed as N grows
-("strong" scaling).
+are column shards, o/down row shards cut out of the compressed arrays, with an all-reduce of the
+activations after o and down (a one-shot kernel over peer memory, NCCL where that is unavailable);
+every rank decodes only its own shard.  Total work is fixed as N grows ("strong" scaling).
 
 --impl reference times the CPU restatement of the reference's algorithm (the oracle; the reference
 ships no CPU codec) on the host cores, on the same workload, metric and unit.
@@ -135,21 +135,25 @@ def build_block(rank, world, device):
     return mods, wbytes, notes
 
 
+REDUCER = None          # collective.OneShotAllReduce of this rank (N > 1), set by run_ours
+
+
 def block_step(mods, x, world):
     """One token batch through the seven linears (attention and the SwiGLU product are outside the hot
     path and left out; the data flow between the layers is real)."""
     import torch.distributed as dist
+    reduce = REDUCER if REDUCER is not None else dist.all_reduce
     q = mods["q_proj"](x)
     mods["k_proj"](x)
     mods["v_proj"](x)
     h = mods["o_proj"](q)                       # column shard of q feeds the row shard of o
     if world > 1:
-        dist.all_reduce(h)
+        reduce(h)
     g = mods["gate_proj"](h)
     mods["up_proj"](h)
     y = mods["down_proj"](g)
     if world > 1:
-        dist.all_reduce(y)
+        reduce(y)
     return y
 
 
@@ -306,6 +310,12 @@ def run_ours(args):
         trace("process group up")
     M = args.batch
     mods, wbytes, notes = build_block(rank, world, device)
+    if world > 1:
+        global REDUCER
+        from comp_inference_b200.collective import OneShotAllReduce
+        REDUCER = OneShotAllReduce(capacity=16 * HIDDEN, device=device)
+        notes.append("activation all-reduce: one-shot over peer memory" if REDUCER.native
+                     else f"activation all-reduce: NCCL ({REDUCER.why})")
     trace("weights compressed and sharded")
 
     gen = torch.Generator().manual_seed(2000 + M)

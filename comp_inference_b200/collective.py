@@ -1,0 +1,66 @@
+"""Tensor-parallel exchange: a one-shot all-reduce over peer memory for the small activation tensors
+that row-parallel linears produce (ci_allreduce_oneshot), with NCCL as the route for anything that does
+not fit it.  The reference has no multi-GPU code.
+
+The buffers every peer writes into come from torch's symmetric memory (CUDA IPC / fabric handles mapped
+into each process); only plain peer loads and stores are used on them.
+"""
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class OneShotAllReduce:
+    """all_reduce(sum) for bf16 tensors of at most ``capacity`` elements on ``group``; in place.
+
+    Falls back to ``dist.all_reduce`` for larger tensors, other dtypes, or when symmetric memory cannot be
+    set up on this system (``self.native`` is then False and ``self.why`` says why)."""
+
+    def __init__(self, group=None, capacity: int = 1 << 16, device=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.capacity = (int(capacity) + 7) // 8 * 8
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.native, self.why = False, ""
+        if self.world == 1:
+            self.why = "single rank"
+            return
+        if self.world > 8:
+            self.why = "more than 8 ranks"
+            return
+        try:
+            import torch.distributed._symmetric_memory as symm
+            lib = _lib.load()
+            total = lib.ci_allreduce_buffer_bytes(self.world, self.capacity)
+            self._buf = symm.empty(total, dtype=torch.uint8, device=self.device)
+            self._buf.zero_()
+            torch.cuda.synchronize(self.device)
+            name = self.group.group_name if hasattr(self.group, "group_name") else self.group
+            self._hdl = symm.rendezvous(self._buf, name)
+            ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+            self._bufs = (C.c_void_p * self.world)(*ptrs)
+            self._counters = torch.zeros(lib.ci_allreduce_counter_bytes(), dtype=torch.uint8, device=self.device)
+            self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            dist.barrier(self.group)                           # every rank's buffer is zeroed before anyone writes
+            torch.cuda.synchronize(self.device)
+            self.native = True
+        except Exception as e:                                  # no peer access, no symmetric memory, ...
+            self.why = f"{type(e).__name__}: {e}"
+
+    def status(self) -> int:
+        """0, or 9 if a wait for a peer ran out (reading it synchronises with the device)."""
+        return int(self._status.item()) if self.native else 0
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        if (not self.native or t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous()
+                or t.numel() > self.capacity):
+            if self.world > 1:
+                dist.all_reduce(t, group=self.group)
+            return t
+        _lib.check(_lib.load().ci_allreduce_oneshot(_lib.ptr(t), _lib.ptr(t), t.numel(), self.capacity, self._bufs,
+                                                    _lib.ptr(self._counters), self.rank, self.world,
+                                                    _lib.ptr(self._status), _lib.stream()))
+        return t

@@ -240,9 +240,10 @@ class RansRowParallelLinear(RansLinear):
     slice and the partial outputs are summed over the group -- the only exchange of a tensor-parallel
     block, on activations; compressed weights never move.  The bias is added once, after the sum."""
 
-    def __init__(self, *args, group=None, **kw):
+    def __init__(self, *args, group=None, reducer=None, **kw):
         super().__init__(*args, **kw)
         self.group = group
+        self.reducer = reducer          # e.g. collective.OneShotAllReduce; None = NCCL all-reduce
 
     def forward(self, x):
         import torch.distributed as dist
@@ -251,7 +252,10 @@ class RansRowParallelLinear(RansLinear):
             y = super().forward(x)
         finally:
             self.bias = bias
-        dist.all_reduce(y, group=self.group)
+        if self.reducer is not None:
+            self.reducer(y)
+        else:
+            dist.all_reduce(y, group=self.group)
         if bias is not None:
             y += bias
         return y
@@ -299,7 +303,7 @@ def _shard(c, kind, rank, world, device):
 
 
 def patch_model_tensor_parallel(model, state_dict, rank, world, group=None, layer_configs=None, default_th=1024,
-                                default_tw=32, device=None):
+                                default_tw=32, device=None, oneshot_rows=16):
     """patch_model for one rank of a tensor-parallel group.  q/k/v/gate/up projections are cut column-wise
     (each rank owns a slice of the heads / of the FFN width), o/down projections row-wise with an all-reduce
     of their outputs; embedding, LM head and every uncompressed parameter are replicated.  The attention
@@ -307,6 +311,13 @@ def patch_model_tensor_parallel(model, state_dict, rank, world, group=None, laye
     from the tensors they are handed.  Returns the model, moved to ``device``."""
     layer_configs = layer_configs or {}
     device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    reducer = None
+    if world > 1 and oneshot_rows:
+        # outputs of up to `oneshot_rows` activation rows go through the peer-memory all-reduce, larger ones
+        # (prefill) through NCCL; the reducer itself falls back to NCCL where peer memory is not available
+        from .collective import OneShotAllReduce
+        width = max((m.out_features for m in model.modules() if isinstance(m, nn.Linear)), default=0)
+        reducer = OneShotAllReduce(group, capacity=oneshot_rows * width, device=device)
     sharded = {}
     for name, module in list(model.named_modules()):
         if not isinstance(module, nn.Linear) or f"{name}.rans_exp_stream" not in state_dict:
@@ -321,7 +332,8 @@ def patch_model_tensor_parallel(model, state_dict, rank, world, group=None, laye
         k, n = c["shape"]
         has_bias = module.bias is not None
         if kind == "row":
-            new = RansRowParallelLinear(k, n, c["tile_height"], c["tile_width"], 1, has_bias, group=group)
+            new = RansRowParallelLinear(k, n, c["tile_height"], c["tile_width"], 1, has_bias, group=group,
+                                        reducer=reducer)
         else:
             new = RansLinear(k, n, c["tile_height"], c["tile_width"], 1, has_bias)
         new.load_compressed(c)

@@ -250,6 +250,21 @@ int ci_encode_legacy_sizes(const uint8_t *d_data, uint64_t n, uint32_t num_strea
 int ci_encode_legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
                            const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len, ci_stream_t stream);
 
+/* ---- tensor-parallel exchange ---------------------------------------------- */
+
+/* One-shot all-reduce (sum) of a small bf16 tensor over peer memory, for the outputs of row-parallel linears.
+ * No counterpart in the reference (it has no multi-GPU code); a tensor-parallel port of it would call an NCCL
+ * all-reduce here.  Every rank owns a buffer of ci_allreduce_buffer_bytes(world, capacity) bytes that all peers
+ * can write (CUDA IPC / symmetric memory), zeroed once, plus ci_allreduce_counter_bytes() of zeroed local memory.
+ * peer_bufs is a host array of `world` device pointers: rank q's buffer as mapped into this process (entry `rank`
+ * is the local one).  capacity (elements) must be a multiple of 8.  Every rank must make the same sequence of
+ * calls; a rank that waits longer than a few seconds for a peer sets *d_status to 9 and returns garbage instead
+ * of hanging.  d_in == d_out is allowed. */
+size_t ci_allreduce_buffer_bytes(uint32_t world, uint32_t capacity);
+size_t ci_allreduce_counter_bytes(void);
+int ci_allreduce_oneshot(const uint16_t *d_in, uint16_t *d_out, uint32_t n, uint32_t capacity, void *const *peer_bufs,
+                         uint32_t *d_counters, uint32_t rank, uint32_t world, uint32_t *d_status, ci_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -97,3 +97,27 @@ def test_tensor_parallel_logits(tmp_path):
             out += "\n[timed out]"
         outs.append(out)
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_oneshot_allreduce():
+    """The peer-memory all-reduce against NCCL on two ranks: several sizes, repeated calls, graph replay."""
+    import socket
+    import subprocess
+    import sys
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = str(s.getsockname()[1])
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ar_worker.py")
+    procs = [subprocess.Popen([sys.executable, worker, str(r), "2", port], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n[timed out]"
+        outs.append(out)
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
