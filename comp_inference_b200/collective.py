@@ -47,8 +47,27 @@ class OneShotAllReduce:
             dist.barrier(self.group)                           # every rank's buffer is zeroed before anyone writes
             torch.cuda.synchronize(self.device)
             self.native = True
+            self._self_test()
         except Exception as e:                                  # no peer access, no symmetric memory, ...
+            self.native = False
             self.why = f"{type(e).__name__}: {e}"
+
+    def _self_test(self):
+        """Two small exchanges checked against NCCL before the first real use; every rank takes the same
+        verdict, so either all of them use the peer-memory kernel or none does."""
+        ok = True
+        for n in (min(self.capacity, 4096), 3):
+            x = (torch.arange(n, device=self.device, dtype=torch.float32) % 13 - 6 + self.rank).to(torch.bfloat16)
+            want = x.clone()
+            dist.all_reduce(want, group=self.group)
+            got = self(x.clone())
+            torch.cuda.synchronize(self.device)
+            ok = ok and bool(torch.equal(got, want)) and self.status() == 0     # small integers: sums are exact
+        verdict = torch.tensor([1 if ok else 0], device=self.device, dtype=torch.int32)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=self.group)
+        if int(verdict.item()) == 0:
+            self.native = False
+            self.why = "self-test against NCCL failed on some rank"
 
     def status(self) -> int:
         """0, or 9 if a wait for a peer ran out (reading it synchronises with the device)."""

@@ -22,7 +22,7 @@ namespace ci {
 constexpr uint32_t kArCtas = 8;
 constexpr uint32_t kArThreads = 256;
 constexpr uint32_t kArMaxWorld = 8;
-constexpr uint32_t kArPolls = 1u << 24;
+constexpr uint32_t kArPolls = 1u << 21;      // about a second of polling before a wait gives up
 
 struct ArArgs {
     uint16_t *bufs[kArMaxWorld];       // every rank's buffer, as mapped into this process
