@@ -127,7 +127,10 @@ def build_block(rank, world, device):
             notes.append(f"{name}: per-rank compression (K/{world} not tile aligned)")
         del Wkn
         k, n = c["shape"]
-        m = ci.RansLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
+        if world > 1 and kind == "row":     # multiplies its row shard and all-reduces the output (reducer set later)
+            m = ci.RansRowParallelLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
+        else:
+            m = ci.RansLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
         mods[name] = m
         wbytes += sum(c[key].numel() * c[key].element_size() for key in
                       ("rans_exp_stream", "rans_exp_states", "rans_exp_tile_offsets", "rans_exp_tile_max_lens",
@@ -135,26 +138,18 @@ def build_block(rank, world, device):
     return mods, wbytes, notes
 
 
-REDUCER = None          # collective.OneShotAllReduce of this rank (N > 1), set by run_ours
-
-
 def block_step(mods, x, world):
     """One token batch through the seven linears (attention and the SwiGLU product are outside the hot
-    path and left out; the data flow between the layers is real)."""
-    import torch.distributed as dist
-    reduce = REDUCER if REDUCER is not None else dist.all_reduce
+    path and left out; the data flow between the layers is real).  With N > 1, o_proj and down_proj are
+    RansRowParallelLinear: they all-reduce their output themselves (inside the GEMV kernel for one or two
+    rows, else with the one-shot kernel or NCCL)."""
     q = mods["q_proj"](x)
     mods["k_proj"](x)
     mods["v_proj"](x)
     h = mods["o_proj"](q)                       # column shard of q feeds the row shard of o
-    if world > 1:
-        reduce(h)
     g = mods["gate_proj"](h)
     mods["up_proj"](h)
-    y = mods["down_proj"](g)
-    if world > 1:
-        reduce(y)
-    return y
+    return mods["down_proj"](g)
 
 
 def secondary_metrics(mods, device):
@@ -311,11 +306,15 @@ def run_ours(args):
     M = args.batch
     mods, wbytes, notes = build_block(rank, world, device)
     if world > 1:
-        global REDUCER
         from comp_inference_b200.collective import OneShotAllReduce
-        REDUCER = OneShotAllReduce(capacity=16 * HIDDEN, device=device)
-        notes.append("activation all-reduce: one-shot over peer memory" if REDUCER.native
-                     else f"activation all-reduce: NCCL ({REDUCER.why})")
+        reducer = OneShotAllReduce(capacity=16 * HIDDEN, device=device)
+        for m in mods.values():
+            if hasattr(m, "reducer"):
+                m.reducer = reducer
+                m._fusable = not args.no_fuse_exchange
+        how = "one-shot kernel behind the GEMV" if args.no_fuse_exchange else "fused into the row-parallel GEMV"
+        notes.append(f"activation all-reduce over peer memory, {how}" if reducer.native
+                     else f"activation all-reduce: NCCL ({reducer.why})")
     trace("weights compressed and sharded")
 
     gen = torch.Generator().manual_seed(2000 + M)
@@ -455,6 +454,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-fuse-exchange", action="store_true",
+                    help="N > 1: all-reduce with the one-shot kernel behind the row-parallel GEMV instead of inside it")
     ap.add_argument("--kernels-once", action="store_true",
                     help="run each hot kernel three times on one 4096x4096 weight and exit (the ncu capture case)")
     args = ap.parse_args()

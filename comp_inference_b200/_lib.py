@@ -77,6 +77,9 @@ SIGNATURES = {
     "ci_encode_legacy_write": (C.c_int, [_V, C.c_uint64, C.c_uint32, _V, _V, _V, C.c_uint64, _S]),
     "ci_allreduce_buffer_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
     "ci_allreduce_counter_bytes": (C.c_size_t, []),
+    "ci_linear_allreduce_counter_bytes": (C.c_size_t, []),
+    "ci_linear_allreduce": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, _V, C.c_size_t, _V,
+                                      C.c_uint32, _V, C.c_uint32, C.c_uint32, _V, _S]),
     "ci_allreduce_oneshot": (C.c_int, [_V, _V, C.c_uint32, C.c_uint32, _V, _V, C.c_uint32, C.c_uint32, _V, _S]),
 }
 

@@ -44,6 +44,14 @@ class OneShotAllReduce:
             self._bufs = (C.c_void_p * self.world)(*ptrs)
             self._counters = torch.zeros(lib.ci_allreduce_counter_bytes(), dtype=torch.uint8, device=self.device)
             self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            # a second buffer with its own call sequence for the exchange fused into the row-parallel GEMV
+            self._buf_f = symm.empty(total, dtype=torch.uint8, device=self.device)
+            self._buf_f.zero_()
+            torch.cuda.synchronize(self.device)
+            self._hdl_f = symm.rendezvous(self._buf_f, name)
+            self._bufs_f = (C.c_void_p * self.world)(*[int(p) for p in self._hdl_f.buffer_ptrs])
+            self._counter_f = torch.zeros(lib.ci_linear_allreduce_counter_bytes(), dtype=torch.uint8,
+                                          device=self.device)
             dist.barrier(self.group)                           # every rank's buffer is zeroed before anyone writes
             torch.cuda.synchronize(self.device)
             self.native = True
@@ -72,6 +80,26 @@ class OneShotAllReduce:
     def status(self) -> int:
         """0, or 9 if a wait for a peer ran out (reading it synchronises with the device)."""
         return int(self._status.item()) if self.native else 0
+
+    def fused_linear(self, w, x2: torch.Tensor, n_out: int, bias=None):
+        """y = all_reduce(x2 @ W_shard) (+ bias) in one kernel (ci_linear_allreduce) for one or two activation
+        rows; returns None when this route does not apply (the caller then multiplies and reduces separately).
+        ``w`` is the ci_tiled_weight descriptor of this rank's row shard."""
+        M = x2.shape[0]
+        if not self.native or M > 2 or n_out % 2 or M * n_out > self.capacity:
+            return None
+        from . import ops
+        lib = _lib.load()
+        y = torch.empty((M, n_out), device=x2.device, dtype=torch.bfloat16)
+        ws = _lib.workspace(x2.device, lib.ci_linear_workspace_bytes(M, n_out, w.K, w.tile_h))
+        b = ops._bias(bias, n_out)
+        rc = lib.ci_linear_allreduce(w, _lib.ptr(x2), x2.stride(0), M, _lib.ptr(b), _lib.ptr(y), _lib.ptr(ws),
+                                     ws.numel(), self._bufs_f, self.capacity, _lib.ptr(self._counter_f), self.rank,
+                                     self.world, _lib.ptr(self._status), _lib.stream())
+        if rc == -1:                                            # CI_E_INVALID: the weight does not qualify
+            return None
+        _lib.check(rc)
+        return y
 
     def __call__(self, t: torch.Tensor) -> torch.Tensor:
         if (not self.native or t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous()

@@ -348,8 +348,9 @@ size_t ci_linear_workspace_bytes(uint32_t M, uint32_t n_out, uint32_t K, uint32_
     return small > big ? small : big;
 }
 
-int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M, const uint16_t *d_bias,
-              uint16_t *d_y, int64_t ldy, void *d_ws, size_t ws_bytes, uint32_t split_k, ci_stream_t stream) {
+static int linear_impl(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M, const uint16_t *d_bias,
+                       uint16_t *d_y, int64_t ldy, void *d_ws, size_t ws_bytes, uint32_t split_k, const ArFuse *ar,
+                       ci_stream_t stream) {
     int rc = check_weight(w, true);
     if (rc) return rc;
     CI_REQUIRE(d_x && d_y, "null activation / output pointer");
@@ -368,6 +369,21 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
     a.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d_ws) + kTicketBytes * 4);
     a.bias = d_bias; a.ldx = ldx; a.ldy = ldy;
     cudaStream_t s = (cudaStream_t)stream;
+    if (ar != nullptr) {
+        // output all-reduced inside the kernel: only the staged GEMV kernels do that, for one or two rows
+        CI_REQUIRE(M <= 2 && split_k == 0 && have_ws, "the fused exchange takes at most two activation rows and needs a workspace");
+        CI_REQUIRE(w->N % 2 == 0 && (uint64_t)M * w->N <= ar->capacity, "output does not fit the exchange buffer");
+        CI_REQUIRE(ldy == (int64_t)w->N, "the fused exchange writes a dense [M, N] output");
+        a.ar = *ar;
+        a.x = d_x; a.y = d_y; a.M = M;
+        rc = launch_linear_mma4(a, w->max_tile_len, s);
+        if (rc == 1) rc = launch_linear_mma(a, w->max_tile_len, s);
+        if (rc == 1) {
+            set_error("this weight does not qualify for the staged kernels the fused exchange lives in");
+            return CI_E_INVALID;
+        }
+        return rc;
+    }
     if (M > 16 && d_ws != nullptr && ws_bytes > (size_t)kTicketBytes * 4) {
         // prefill: tcgen05 decode-GEMM over all rows at once (split_k: 0 = library's choice)
         a.x = d_x; a.y = d_y; a.M = M;
@@ -398,6 +414,29 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
         if (rc) return rc;
     }
     return CI_OK;
+}
+
+int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M, const uint16_t *d_bias,
+              uint16_t *d_y, int64_t ldy, void *d_ws, size_t ws_bytes, uint32_t split_k, ci_stream_t stream) {
+    return linear_impl(w, d_x, ldx, M, d_bias, d_y, ldy, d_ws, ws_bytes, split_k, nullptr, stream);
+}
+
+size_t ci_linear_allreduce_counter_bytes(void) { return 2 * sizeof(uint32_t); }
+
+int ci_linear_allreduce(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M, const uint16_t *d_bias,
+                        uint16_t *d_y, void *d_ws, size_t ws_bytes, void *const *peer_bufs, uint32_t capacity,
+                        uint32_t *d_counter, uint32_t rank, uint32_t world, uint32_t *d_status, ci_stream_t stream) {
+    CI_REQUIRE(w != nullptr && peer_bufs && d_counter, "null pointer");
+    CI_REQUIRE(world >= 2 && world <= kFuseMaxWorld && rank < world, "world size %u / rank %u out of range", world, rank);
+    CI_REQUIRE(capacity % 8 == 0, "capacity must be a multiple of 8 elements");
+    ArFuse ar;
+    memset(&ar, 0, sizeof ar);
+    for (uint32_t q = 0; q < world; ++q) {
+        CI_REQUIRE(peer_bufs[q] != nullptr, "null peer pointer for rank %u", q);
+        ar.bufs[q] = reinterpret_cast<uint16_t *>(peer_bufs[q]);
+    }
+    ar.counter = d_counter; ar.status = d_status; ar.rank = rank; ar.world = world; ar.capacity = capacity;
+    return linear_impl(w, d_x, ldx, M, d_bias, d_y, (int64_t)w->N, d_ws, ws_bytes, 0, &ar, stream);
 }
 
 int ci_linear_transposed(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M,

@@ -1,6 +1,7 @@
 // Shared declarations of the fused decode + linear kernels.
 #pragma once
 #include "common.cuh"
+#include "ar_fuse.cuh"
 
 namespace ci {
 
@@ -25,6 +26,7 @@ struct LinArgs {
     const uint32_t *dense_sizes, *dense_offsets;   // dense layout only
     uint32_t *tickets;   // [items along the non-reduced dimension]
     float *partial;      // [splits][M][n_out]
+    ArFuse ar;           // ar.world > 1: all-reduce the output over the ranks inside the kernel (M <= 2)
 };
 
 struct LaneTile {

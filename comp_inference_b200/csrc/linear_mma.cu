@@ -144,6 +144,8 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (lo >= hi) return;                                       // no CTA-wide synchronisation below this line
+    const bool fused_ar = a.ar.world > 1;                       // row-parallel: exchange the sums with the peers here
+    const uint32_t ar_seq = fused_ar ? fuse_seq(a.ar) : 0u;
 
     float acc[4][4];
     auto zero_acc = [&]() {
@@ -171,6 +173,19 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
             }
         };
         if (count == 1) {
+            if (fused_ar) {                                     // M <= 2: rows 0 / 1 live in the lanes with r0 < M
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb) {
+                    const uint32_t n = grp * 32 + nb * 8 + c0;
+                    if (r0 < a.M && n < g.N) {
+                        const float2 r = fuse_exchange_pair(a.ar, ar_seq, (r0 * g.N + n) / 2, acc[nb][0], acc[nb][1]);
+                        acc[nb][0] = r.x;
+                        acc[nb][1] = r.y;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) fuse_group_done(a.ar, ar_seq, g.groups);
+            }
 #pragma unroll
             for (int nb = 0; nb < 4; ++nb) {
                 store_y(r0, grp * 32 + nb * 8 + c0, acc[nb][0], acc[nb][1]);
@@ -215,6 +230,18 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
                 }
             }
             const uint32_t n = grp * 32 + lane;
+            if (fused_ar) {                                     // even lanes exchange (n, n + 1) of both rows
+                const float o0 = __shfl_down_sync(kFull, s0, 1), o1 = __shfl_down_sync(kFull, s1, 1);
+                float2 r0x = make_float2(s0, o0), r1x = make_float2(s1, o1);
+                if ((lane & 1) == 0 && n < g.N) {
+                    r0x = fuse_exchange_pair(a.ar, ar_seq, n / 2, s0, o0);
+                    if (two) r1x = fuse_exchange_pair(a.ar, ar_seq, (g.N + n) / 2, s1, o1);
+                }
+                const float u0 = __shfl_up_sync(kFull, r0x.y, 1), u1 = __shfl_up_sync(kFull, r1x.y, 1);
+                s0 = (lane & 1) ? u0 : r0x.x;
+                s1 = (lane & 1) ? u1 : r1x.x;
+                if (lane == 0) fuse_group_done(a.ar, ar_seq, g.groups);
+            }
             if (n < g.N) {
                 const float b = a.bias ? load_bf16(a.bias + n) : 0.f;
                 a.y[n] = float_to_bf16_bits(s0 + b);

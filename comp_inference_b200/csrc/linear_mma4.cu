@@ -207,6 +207,8 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (lo >= hi) return;                                       // no CTA-wide synchronisation below this line
+    const bool fused_ar = a.ar.world > 1;                       // row-parallel: exchange the sums with the peers here
+    const uint32_t ar_seq = fused_ar ? fuse_seq(a.ar) : 0u;
 
     float acc[4][4];
     auto zero_acc = [&]() {
@@ -256,6 +258,18 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             v1[4 + j] = acc[j][3];
         }
         if (count == 1) {
+            if (fused_ar) {                                     // M <= 2: rows 0 / 1 live in the lanes with gq < M
+                if (gq < a.M && n0 < g.N) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 r = fuse_exchange_pair(a.ar, ar_seq, (gq * g.N + n0) / 2 + j, v0[2 * j], v0[2 * j + 1]);
+                        v0[2 * j] = r.x;
+                        v0[2 * j + 1] = r.y;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) fuse_group_done(a.ar, ar_seq, g.groups);
+            }
             store_row(gq, v0);
             store_row(gq + 8, v1);
             return;
@@ -298,6 +312,18 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
                 }
             }
             const uint32_t n = grp * 32 + lane;
+            if (fused_ar) {                                     // even lanes exchange (n, n + 1) of both rows
+                const float o0 = __shfl_down_sync(kFull, s0, 1), o1 = __shfl_down_sync(kFull, s1, 1);
+                float2 r0 = make_float2(s0, o0), r1 = make_float2(s1, o1);
+                if ((lane & 1) == 0 && n < g.N) {
+                    r0 = fuse_exchange_pair(a.ar, ar_seq, n / 2, s0, o0);
+                    if (two) r1 = fuse_exchange_pair(a.ar, ar_seq, (g.N + n) / 2, s1, o1);
+                }
+                const float u0 = __shfl_up_sync(kFull, r0.y, 1), u1 = __shfl_up_sync(kFull, r1.y, 1);
+                s0 = (lane & 1) ? u0 : r0.x;
+                s1 = (lane & 1) ? u1 : r1.x;
+                if (lane == 0) fuse_group_done(a.ar, ar_seq, g.groups);
+            }
             if (n < g.N) {
                 const float b = a.bias ? load_bf16(a.bias + n) : 0.f;
                 a.y[n] = float_to_bf16_bits(s0 + b);

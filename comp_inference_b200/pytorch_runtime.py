@@ -238,15 +238,31 @@ _ROW_PARALLEL = ("o_proj", "down_proj")
 class RansRowParallelLinear(RansLinear):
     """Row shard (a slice of the input features) of a compressed linear: every rank multiplies its
     slice and the partial outputs are summed over the group -- the only exchange of a tensor-parallel
-    block, on activations; compressed weights never move.  The bias is added once, after the sum."""
+    block, on activations; compressed weights never move.  The bias is added once, after the sum.
 
-    def __init__(self, *args, group=None, reducer=None, **kw):
+    ``reducer``: a collective.OneShotAllReduce (peer-memory kernel) or None (NCCL).  ``fuse_exchange``: for one
+    or two activation rows run ci_linear_allreduce, i.e. let the GEMV's final-reduction warps push their sums to
+    the peers themselves instead of writing a partial output for a second kernel.  On 2 B200s the two routes are
+    within 1 % of each other (the separate kernel overlaps with the next kernel's preamble and synchronises the
+    ranks once instead of once per column group); more activation rows always take the separate route."""
+
+    def __init__(self, *args, group=None, reducer=None, fuse_exchange=True, **kw):
         super().__init__(*args, **kw)
         self.group = group
         self.reducer = reducer          # e.g. collective.OneShotAllReduce; None = NCCL all-reduce
+        self._fusable = bool(fuse_exchange)
 
     def forward(self, x):
         import torch.distributed as dist
+        fused = getattr(self.reducer, "fused_linear", None)
+        if fused is not None and self._fusable:
+            K, N = self.in_features, self.out_features
+            x2 = ops._check_x(x, K)
+            if x2.shape[0] <= 2:                                # decode steps: multiply and exchange in one kernel
+                y = fused(self._weight(K, N), x2, N, self.bias)
+                if y is not None:
+                    return y.view(*x.shape[:-1], N)
+                self._fusable = False                           # this weight does not qualify: do not ask again
         bias, self.bias = self.bias, None
         try:
             y = super().forward(x)

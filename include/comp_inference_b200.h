@@ -265,6 +265,19 @@ size_t ci_allreduce_counter_bytes(void);
 int ci_allreduce_oneshot(const uint16_t *d_in, uint16_t *d_out, uint32_t n, uint32_t capacity, void *const *peer_bufs,
                          uint32_t *d_counters, uint32_t rank, uint32_t world, uint32_t *d_status, ci_stream_t stream);
 
+/* Row-parallel fused decode-linear with the all-reduce inside the kernel: y[M, N] = sum over ranks of
+ * x_rank[M, K_rank] . W_rank[K_rank, N] (+ bias, added once after the sum).  The warps that hold a column group's
+ * final sums push them into every peer's exchange buffer and add the peers' (same tagged 8-byte protocol and
+ * buffer size as ci_allreduce_oneshot; use a buffer of its own), so no partial output is written and no second
+ * kernel runs.  M <= 2, N even, M * N <= capacity, dense output rows; d_counter: ci_linear_allreduce_counter_bytes()
+ * of zeroed local memory.  Returns CI_E_INVALID when the weight does not qualify for the staged GEMV kernels
+ * (the caller then runs ci_linear followed by ci_allreduce_oneshot).  No counterpart in the reference. */
+size_t ci_linear_allreduce_counter_bytes(void);
+int ci_linear_allreduce(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M,
+                        const uint16_t *d_bias, uint16_t *d_y, void *d_workspace, size_t workspace_bytes,
+                        void *const *peer_bufs, uint32_t capacity, uint32_t *d_counter, uint32_t rank, uint32_t world,
+                        uint32_t *d_status, ci_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

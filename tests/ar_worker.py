@@ -52,9 +52,37 @@ def main():
     if float((y.float() - want.float()).abs().max()) > 2.0 ** -6 * max(float(want.float().abs().max()), 1.0):
         ok = False
         print(f"rank {rank}: graph replay mismatch", flush=True)
-    if ar.status() != 0:
+    # the exchange fused into the row-parallel GEMV: each rank holds a row shard of W, both kernels
+    # (small matrix -> one-tile units, large matrix -> two-tile units), one and two activation rows, repeated
+    import comp_inference_b200 as ci
+    from comp_inference_b200 import _lib
+    for (K, N) in ((1024, 256), (4096, 4096)):
+        gw = torch.Generator().manual_seed(7)
+        W = (torch.randn(K, N, generator=gw) * 0.02).to(torch.bfloat16)
+        k = K // world
+        c = ci.compress_weight_cuda(W[rank * k:(rank + 1) * k].contiguous().cuda(), 128, 32)
+        lin = ci.RansRowParallelLinear(k, N, c["tile_height"], c["tile_width"], reducer=ar,
+                                       fuse_exchange=True).load_compressed(c).cuda()
+        for M in (1, 2):
+            xs = torch.randn(M, K, generator=gw).to(torch.bfloat16)
+            ref = xs.double() @ W.double()
+            for rep in range(3):
+                y = lin(xs[:, rank * k:(rank + 1) * k].contiguous().cuda())
+                torch.cuda.synchronize()
+                err = float((y.double().cpu() - ref).abs().max() / ref.abs().max())
+                if err > 2e-2 or not lin._fusable:
+                    ok = False
+                    print(f"rank {rank}: fused K={K} N={N} M={M} rep={rep} err {err} fusable {lin._fusable}", flush=True)
+        # every rank must hold the same result
+        mine = y.float().clone()
+        other = mine.clone()
+        dist.broadcast(other, src=0)
+        if not torch.equal(mine, other):
+            ok = False
+            print(f"rank {rank}: ranks disagree on the fused result", flush=True)
+    if ar.status() != 0 or _lib.kernel_status(f"cuda:{rank}") != 0:
         ok = False
-        print(f"rank {rank}: status {ar.status()}", flush=True)
+        print(f"rank {rank}: status {ar.status()} / {_lib.kernel_status(f'cuda:{rank}')}", flush=True)
     del graph
     dist.barrier()
     torch.cuda.synchronize()
