@@ -308,14 +308,33 @@ def run_ours(args):
     if world > 1:
         from comp_inference_b200.collective import OneShotAllReduce
         reducer = OneShotAllReduce(capacity=16 * HIDDEN, device=device)
-        for m in mods.values():
-            if hasattr(m, "reducer"):
-                m.reducer = reducer
-                m._fusable = not args.no_fuse_exchange
-        how = "one-shot kernel behind the GEMV" if args.no_fuse_exchange else "fused into the row-parallel GEMV"
+        row_mods = [m for m in mods.values() if hasattr(m, "reducer")]
+        for m in row_mods:
+            m.reducer = reducer
+            m._fusable = False
+        fuse = reducer.native and not args.no_fuse_exchange
+        if fuse:
+            # one step each way before anything is timed: the fused exchange must reproduce the separate one on
+            # every rank, else all ranks drop it together
+            xt = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(77)).to(torch.bfloat16).to(device)
+            y_sep = block_step(mods, xt, world).float()
+            for m in row_mods:
+                m._fusable = True
+            y_fused = block_step(mods, xt, world).float()
+            torch.cuda.synchronize()
+            from comp_inference_b200 import _lib as _cl
+            good = (float((y_fused - y_sep).abs().max()) <= 3e-2 * max(float(y_sep.abs().max()), 1e-6)
+                    and reducer.status() == 0 and _cl.kernel_status(device) == 0)
+            verdict = torch.tensor([1 if good else 0], device=device, dtype=torch.int32)
+            dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+            fuse = bool(verdict.item())
+            for m in row_mods:
+                m._fusable = fuse
+            if not fuse:
+                notes.append("fused exchange failed its check against the separate one: not used")
+        how = "fused into the row-parallel GEMV" if fuse else "one-shot kernel behind the GEMV"
         notes.append(f"activation all-reduce over peer memory, {how}" if reducer.native
                      else f"activation all-reduce: NCCL ({reducer.why})")
-    trace("weights compressed and sharded")
 
     gen = torch.Generator().manual_seed(2000 + M)
     x_host = torch.randn(M, HIDDEN, generator=gen).to(torch.bfloat16).pin_memory()
