@@ -79,8 +79,9 @@ def test_tensor_parallel_logits(tmp_path):
     ids = torch.randint(0, cfg.vocab_size, (2, 16), generator=torch.Generator().manual_seed(4001))
     with torch.no_grad():
         logits = single(ids.cuda()).logits.float().cpu()
+        logits1 = single(ids[:, :1].cuda()).logits.float().cpu()
     ref_path = str(tmp_path / "ref.pt")
-    torch.save({"ids": ids, "logits": logits}, ref_path)
+    torch.save({"ids": ids, "logits": logits, "logits1": logits1}, ref_path)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = str(s.getsockname()[1])

@@ -38,6 +38,13 @@ def main():
     agree = float((logits.argmax(-1) == ref["logits"].argmax(-1)).float().mean())
     print(f"rank {rank}: rel err {err:.3e}, argmax agreement {agree:.3f}", flush=True)
     ok = err <= 3e-2 and agree > 0.9
+    # one token per sequence = two activation rows: the row-parallel layers multiply and exchange in one kernel
+    with torch.no_grad():
+        logits1 = model(ref["ids"][:, :1].cuda()).logits.float().cpu()
+    err1 = float((logits1 - ref["logits1"]).abs().max() / ref["logits1"].abs().max())
+    fused = [m._fusable for m in model.modules() if type(m).__name__ == "RansRowParallelLinear"]
+    print(f"rank {rank}: single-token rel err {err1:.3e}, fused layers {sum(fused)}/{len(fused)}", flush=True)
+    ok = ok and err1 <= 3e-2 and all(fused)
     dist.barrier()
     torch.cuda.synchronize()
     os._exit(0 if ok else 1)                  # communicator clean-up is left to process exit
