@@ -11,8 +11,9 @@
 // are one 8-byte load per activation row, and column block c of the lane is mma column n = g.  No
 // shared-memory transpose, no ldmatrix.
 //
-// Shared-memory traffic per decoded symbol is what bounds this kernel, so everything but the table
-// lookup is arranged to be conflict free:
+// What bounds this kernel is integer instruction issue (about 19 integer instructions per decoded
+// symbol on two half-rate pipes), so the data movement around the decode step is arranged to cost
+// as few instructions and shared-memory wavefronts as possible:
 //  * compressed bytes: the two tiles' byte blocks ([row][64 B] each) are copied by cp.async into one
 //    window of 128-byte rows (upper tile in bytes 0..63, lower tile in 64..127).  The four streams of a
 //    lane are the four bytes of one word column, so every lane reads its own bank whatever row each of
