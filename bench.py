@@ -227,15 +227,20 @@ def kernels_once(args):
     g = torch.Generator().manual_seed(7)
     x1 = torch.randn(1, K, generator=g).to(torch.bfloat16).cuda()
     x512 = torch.randn(512, K, generator=g).to(torch.bfloat16).cuda()
+    ids = torch.randint(0, K, (4096,), generator=g).cuda()
     for _ in range(3):
         y1 = m(x1)                                                    # k_linear_mma4
         y512 = m(x512)                                                # k_linear_gemm + k_splitk_reduce
         w = ci.rans_decompress_bf16(m.rans_exp_stream, m.rans_exp_states, m.rans_exp_tables, m.rans_exp_slot_map,
                                     (K, N), m.rans_exp_tile_offsets, m.rans_exp_tile_max_lens, m.tile_k, m.tile_n,
                                     m.rans_man_raw)                   # k_decode4
+        rows = ci.fused_rans_embedding_triton(ids, m.rans_exp_stream, m.rans_exp_states, m.rans_exp_tables,
+                                              m.rans_exp_slot_map, (K, N), m.rans_exp_tile_offsets,
+                                              m.rans_exp_tile_max_lens, m.tile_k, m.tile_n, m.rans_man_raw)  # k_embedding4
     torch.cuda.synchronize()
     ref1, ref512 = x1.float() @ W.float(), x512.float() @ W.float()
     print(json.dumps({"kernels_once": True, "decode_bit_exact": bool(torch.equal(w.view(torch.int16), W.view(torch.int16))),
+                      "embedding_bit_exact": bool(torch.equal(rows.view(torch.int16), W[ids].view(torch.int16))),
                       "gemv_rel_err": float((y1.float() - ref1).abs().max() / ref1.abs().max()),
                       "gemm_rel_err": float((y512.float() - ref512).abs().max() / ref512.abs().max())}))
 

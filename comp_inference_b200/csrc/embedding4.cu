@@ -178,6 +178,7 @@ __global__ void __launch_bounds__(kEmb4Warps * 32, 1) k_embedding4(const __grid_
                 s0 = stC.x; s1 = stC.y; s2 = stC.z; s3 = stC.w;
             }
             if (ok && tc.valid) {
+#pragma unroll 4
                 for (uint32_t i = 0; i < tc.inner; ++i) {        // the rows above the wanted one
                     const uint32_t y0 = lds_u8(pos0), y1 = lds_u8(pos1), y2 = lds_u8(pos2), y3 = lds_u8(pos3);
                     (void)decode_fast(s0, lut_s);
