@@ -93,8 +93,14 @@ __device__ __forceinline__ void renorm4(uint32_t &s0, uint32_t &s1, uint32_t &s2
     }
 }
 
-// Four symbols of each of the lane's streams -> four B fragments -> four mma.  m = sign+mantissa words of
-// the four rows, xf = the activations of those rows (A fragment).
+// Four symbols of each of the lane's streams -> four packed weight pairs per column -> tensor core.
+// m = sign+mantissa words of the four rows, xf = the activations of those rows.
+//  * WA == false (up to 16 activation rows): the weights are the B operand, one mma per column of the lane
+//    (mma column n = g), the activations of rows g and g + 8 the A operand (xf = a0..a3);
+//  * WA == true (up to 8 activation rows): the weights are the A operand -- columns c and c + 1 of the lane
+//    are mma rows g and g + 8, so one mma takes two columns -- and activation row g is the B operand
+//    (xf[0], xf[1]).  Half the mma instructions, half the activation loads, half the accumulators.
+template <bool WA>
 __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_t &s1, uint32_t &s2, uint32_t &s3,
                                        uint32_t &p0, uint32_t &p1, uint32_t &p2, uint32_t &p3, uint32_t lut_s,
                                        const uint32_t (&m)[4], const uint32_t (&xf)[4]) {
@@ -102,40 +108,51 @@ __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_
 #pragma unroll
     for (int h = 0; h < 2; ++h) {                               // two rows -> one packed pair per column
         uint32_t y0 = lds_u8(p0), y1 = lds_u8(p1), y2 = lds_u8(p2), y3 = lds_u8(p3);
-        const uint32_t e0 = decode_fast(s0, lut_s);
-        const uint32_t e1 = decode_fast(s1, lut_s);
-        const uint32_t e2 = decode_fast(s2, lut_s);
-        const uint32_t e3 = decode_fast(s3, lut_s);
+        const uint32_t e0 = decode_aligned(s0, lut_s);
+        const uint32_t e1 = decode_aligned(s1, lut_s);
+        const uint32_t e2 = decode_aligned(s2, lut_s);
+        const uint32_t e3 = decode_aligned(s3, lut_s);
         renorm4(s0, s1, s2, s3, p0, p1, p2, p3, y0, y1, y2, y3);
         y0 = lds_u8(p0);
         y1 = lds_u8(p1);
         y2 = lds_u8(p2);
         y3 = lds_u8(p3);
-        const uint32_t f0 = decode_fast(s0, lut_s);
-        const uint32_t f1 = decode_fast(s1, lut_s);
-        const uint32_t f2 = decode_fast(s2, lut_s);
-        const uint32_t f3 = decode_fast(s3, lut_s);
+        const uint32_t f0 = decode_aligned(s0, lut_s);
+        const uint32_t f1 = decode_aligned(s1, lut_s);
+        const uint32_t f2 = decode_aligned(s2, lut_s);
+        const uint32_t f3 = decode_aligned(s3, lut_s);
         renorm4(s0, s1, s2, s3, p0, p1, p2, p3, y0, y1, y2, y3);
         b[0][h] = weight_pair4<0>(e0, f0, m[2 * h], m[2 * h + 1]);
         b[1][h] = weight_pair4<1>(e1, f1, m[2 * h], m[2 * h + 1]);
         b[2][h] = weight_pair4<2>(e2, f2, m[2 * h], m[2 * h + 1]);
         b[3][h] = weight_pair4<3>(e3, f3, m[2 * h], m[2 * h + 1]);
     }
-    mma_bf16(acc[0], xf, b[0][0], b[0][1]);
-    mma_bf16(acc[1], xf, b[1][0], b[1][1]);
-    mma_bf16(acc[2], xf, b[2][0], b[2][1]);
-    mma_bf16(acc[3], xf, b[3][0], b[3][1]);
+    if constexpr (WA) {
+        const uint32_t w01[4] = {b[0][0], b[1][0], b[0][1], b[1][1]};
+        const uint32_t w23[4] = {b[2][0], b[3][0], b[2][1], b[3][1]};
+        mma_bf16(acc[0], w01, xf[0], xf[1]);
+        mma_bf16(acc[1], w23, xf[0], xf[1]);
+    } else {
+        mma_bf16(acc[0], xf, b[0][0], b[0][1]);
+        mma_bf16(acc[1], xf, b[1][0], b[1][1]);
+        mma_bf16(acc[2], xf, b[2][0], b[2][1]);
+        mma_bf16(acc[3], xf, b[3][0], b[3][1]);
+    }
 }
 
+template <bool WA>
 __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid_constant__ Mma4Args p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs &a = p.a;
     const Geom &g = a.g;
-    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem);
     const uint32_t W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t smem_s = smem_u32(smem);
-    const uint32_t wbase_s = smem_s + kLutBytes + kBar4Bytes + warp * 2 * p.stage_bytes;
-    const uint32_t bar_base = smem_s + kLutBytes + warp * 16;
+    // The table sits on a 16 KB boundary of the shared window, so that an entry's address is
+    // (state << 2 & 0x3FFC) | base: one shift and one three-input logic operation, no addition.
+    const uint32_t lut_s = (smem_s + kLutBytes - 1) & ~(kLutBytes - 1);
+    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem + (lut_s - smem_s));
+    const uint32_t wbase_s = lut_s + kLutBytes + kBar4Bytes + warp * 2 * p.stage_bytes;
+    const uint32_t bar_base = lut_s + kLutBytes + warp * 16;
     const uint32_t seg_bytes = g.th * 16;                       // half a tile of sign+mantissa bytes
     const uint32_t st_off = p.cap_rows * 128;
 
@@ -251,12 +268,30 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             }
         };
         float v0[8], v1[8];
+        if constexpr (WA) {
+            // The D fragments hold columns 4 gq .. 4 gq + 3 of activation rows 2q and 2q + 1
+            // (acc[c / 2][2 (c % 2) + row parity]); bring them into the layout of the other path -- row gq,
+            // columns 8q .. 8q + 7 -- which everything below works on.  Sources: lanes (2q, gq / 2) and
+            // (2q + 1, gq / 2).
+            const uint32_t srcA = (2 * q) * 4 + (gq >> 1), srcB = srcA + 4;
+            const bool odd = gq & 1;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            v0[j] = acc[j][0];
-            v0[4 + j] = acc[j][1];
-            v1[j] = acc[j][2];
-            v1[4 + j] = acc[j][3];
+            for (int c = 0; c < 4; ++c) {
+                const float e0 = acc[c >> 1][2 * (c & 1)], e1 = acc[c >> 1][2 * (c & 1) + 1];
+                const float a0 = __shfl_sync(kFull, e0, srcA), a1 = __shfl_sync(kFull, e1, srcA);
+                const float b0 = __shfl_sync(kFull, e0, srcB), b1 = __shfl_sync(kFull, e1, srcB);
+                v0[c] = odd ? a1 : a0;
+                v0[4 + c] = odd ? b1 : b0;
+                v1[c] = v1[4 + c] = 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v0[j] = acc[j][0];
+                v0[4 + j] = acc[j][1];
+                v1[j] = acc[j][2];
+                v1[4 + j] = acc[j][3];
+            }
         }
         if (count == 1) {
             if (fused_ar) {                                     // M <= 2: rows 0 / 1 live in the lanes with gq < M
@@ -372,7 +407,6 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
     uint32_t parity0 = 0, parity1 = 0, stage = 0;
     uint32_t cur_grp = lo / p.pairs_k;
     zero_acc();
-    const uint32_t lut_s = smem_s;
     const uint32_t n_groups = g.half / 4;                       // 4-symbol groups per stream (even)
 
     uint32_t s0, s1, s2, s3, pos0, pos1, pos2, pos3;
@@ -384,11 +418,17 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 #pragma unroll
         for (int i = 0; i < 4; ++i) m[i] = ldg_stream_u32(mp + i * 32);
         const uint2 v0 = __ldg(reinterpret_cast<const uint2 *>(xp0));
-        const uint2 v1 = __ldg(reinterpret_cast<const uint2 *>(xp1));
-        xf[0] = v0.x;
-        xf[1] = v1.x;
-        xf[2] = v0.y;
-        xf[3] = v1.y;
+        if constexpr (WA) {
+            xf[0] = v0.x;
+            xf[1] = v0.y;
+            xf[2] = xf[3] = 0;
+        } else {
+            const uint2 v1 = __ldg(reinterpret_cast<const uint2 *>(xp1));
+            xf[0] = v0.x;
+            xf[1] = v1.x;
+            xf[2] = v0.y;
+            xf[3] = v1.y;
+        }
     };
 
     for (uint32_t t = lo; t < hi; ++t) {
@@ -453,12 +493,12 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 #pragma unroll 1
         for (uint32_t gi = 0; gi < n_groups; gi += 2) {         // operands are fetched one group ahead
             fetch(mp + 128, xp0 + 4, xp1 + 4, mB, xB);
-            group4(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
+            group4<WA>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
             mp += 256;
             xp0 += 8;
             xp1 += 8;
             if (gi + 2 < n_groups) fetch(mp, xp0, xp1, mA, xA);
-            group4(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
+            group4<WA>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
         }
         stage ^= 1;
     }
@@ -486,7 +526,7 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     p.a = a;
     p.cap_rows = max_tile_len;
     p.stage_bytes = (p.cap_rows * 128u + 512u + 127u) & ~127u;
-    const uint32_t fixed = kLutBytes + kBar4Bytes;
+    const uint32_t fixed = 2 * kLutBytes + kBar4Bytes;         // up to one table size is lost to the table's alignment
     const uint32_t warp_bytes = 2 * p.stage_bytes;
     if ((uint32_t)max_smem < fixed + 4 * warp_bytes) return 1;
     uint32_t w_max = ((uint32_t)max_smem - fixed) / warp_bytes;
@@ -518,7 +558,8 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
 
     static bool attr = false;
     if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_linear_mma4, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+        CI_CUDA(cudaFuncSetAttribute(k_linear_mma4<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+        CI_CUDA(cudaFuncSetAttribute(k_linear_mma4<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
         attr = true;
     }
     // Programmatic dependent launch: the grid may be scheduled while the previous kernel of the stream
@@ -533,7 +574,7 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    CI_CUDA(cudaLaunchKernelEx(&cfg, k_linear_mma4, p));
+    CI_CUDA(cudaLaunchKernelEx(&cfg, a.M <= 8 ? k_linear_mma4<true> : k_linear_mma4<false>, p));
     return CI_OK;
 }
 

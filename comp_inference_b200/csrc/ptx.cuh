@@ -77,6 +77,12 @@ __device__ __forceinline__ uint32_t decode_fast(uint32_t &state, uint32_t lut_s)
     state = (e >> 20) * (state >> kProbBits) + (e & 0xFFFu);
     return e;
 }
+// The same with the table on a 16 KB boundary of the shared window: the entry's address needs no addition.
+__device__ __forceinline__ uint32_t decode_aligned(uint32_t &state, uint32_t lut_s) {
+    const uint32_t e = lds_u32(((state << 2) & ((kProbScale - 1) << 2)) | lut_s);
+    state = (e >> 20) * (state >> kProbBits) + (e & 0xFFFu);
+    return e;
+}
 // Renormalisation, STRIDE bytes between the rows of a stream.
 //
 // No lower-bound test anywhere in this family: a well-formed stream always has a byte left when its
