@@ -50,11 +50,14 @@ __global__ void __launch_bounds__(kDec4Warps * 32, 1) k_decode4(const __grid_con
     extern __shared__ __align__(128) uint8_t smem[];
     const DecArgs &a = p.a;
     const Geom &g = a.g;
-    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem);
     const uint32_t W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t smem_s = smem_u32(smem);
-    const uint32_t wbase_s = smem_s + kLutBytes + kDec4BarBytes + warp * 2 * p.stage_bytes;
-    const uint32_t bar_base = smem_s + kLutBytes + warp * 16;
+    // The table sits on a 16 KB boundary of the shared window: an entry's address is then
+    // (state << 2 & 0x3FFC) | base, without an addition.
+    const uint32_t lut_s = (smem_s + kLutBytes - 1) & ~(kLutBytes - 1);
+    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem + (lut_s - smem_s));
+    const uint32_t wbase_s = lut_s + kLutBytes + kDec4BarBytes + warp * 2 * p.stage_bytes;
+    const uint32_t bar_base = lut_s + kLutBytes + warp * 16;
     const uint32_t st_off = p.cap_rows * 128;
     const uint32_t man_tile = g.th * 32;
 
@@ -126,7 +129,6 @@ __global__ void __launch_bounds__(kDec4Warps * 32, 1) k_decode4(const __grid_con
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    const uint32_t lut_s = smem_s;
     const uint32_t n_groups = g.half / 4;
     uint32_t parity0 = 0, parity1 = 0, stage = 0, li = 0;
     uint32_t s0, s1, s2, s3, pos0, pos1, pos2, pos3;
@@ -212,10 +214,10 @@ __global__ void __launch_bounds__(kDec4Warps * 32, 1) k_decode4(const __grid_con
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const uint32_t y0 = lds_u8(pos0), y1 = lds_u8(pos1), y2 = lds_u8(pos2), y3 = lds_u8(pos3);
-                const uint32_t e0 = decode_fast(s0, lut_s);
-                const uint32_t e1 = decode_fast(s1, lut_s);
-                const uint32_t e2 = decode_fast(s2, lut_s);
-                const uint32_t e3 = decode_fast(s3, lut_s);
+                const uint32_t e0 = decode_aligned(s0, lut_s);
+                const uint32_t e1 = decode_aligned(s1, lut_s);
+                const uint32_t e2 = decode_aligned(s2, lut_s);
+                const uint32_t e3 = decode_aligned(s3, lut_s);
                 renorm4(y0, y1, y2, y3);
                 // bits 8..23 of two entries side by side: the symbols sit at bits 4..11 / 20..27
                 const uint32_t a01 = __byte_perm(e0, e1, 0x6521), a23 = __byte_perm(e2, e3, 0x6521);
@@ -291,7 +293,7 @@ int launch_decode4(const DecArgs &a, uint32_t max_tile_len, bool bf16, void *out
     p.pairs_n = (g.tiles_n + 1) / 2;
     p.total = g.tiles_k * p.pairs_n;
     p.status = nullptr;
-    const uint32_t fixed = kLutBytes + kDec4BarBytes;
+    const uint32_t fixed = 2 * kLutBytes + kDec4BarBytes;           // up to one table size is lost to the table's alignment
     const uint32_t warp_bytes = 2 * p.stage_bytes;
     if ((uint32_t)max_smem < fixed + 4 * warp_bytes) return 1;
     uint32_t w_max = ((uint32_t)max_smem - fixed) / warp_bytes;

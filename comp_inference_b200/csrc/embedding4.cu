@@ -46,11 +46,14 @@ __global__ void __launch_bounds__(kEmb4Warps * 32, 1) k_embedding4(const __grid_
     extern __shared__ __align__(128) uint8_t smem[];
     const EmbArgs &a = p.a;
     const Geom &g = a.g;
-    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem);
     const uint32_t W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = lane_id();
     const uint32_t smem_s = smem_u32(smem);
-    const uint32_t wbase_s = smem_s + kLutBytes + kEmb4BarBytes + warp * 2 * p.stage_bytes;
-    const uint32_t bar_base = smem_s + kLutBytes + warp * 16;
+    // The table sits on a 16 KB boundary of the shared window: an entry's address is then
+    // (state << 2 & 0x3FFC) | base, without an addition.
+    const uint32_t lut_s = (smem_s + kLutBytes - 1) & ~(kLutBytes - 1);
+    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem + (lut_s - smem_s));
+    const uint32_t wbase_s = lut_s + kLutBytes + kEmb4BarBytes + warp * 2 * p.stage_bytes;
+    const uint32_t bar_base = lut_s + kLutBytes + warp * 16;
     const uint64_t gw = (uint64_t)blockIdx.x * W + warp, n_warps = (uint64_t)gridDim.x * W;
     const uint32_t tsel = lane >> 3, quad = lane & 7;           // tile of the block, column quad inside it
 
@@ -121,7 +124,6 @@ __global__ void __launch_bounds__(kEmb4Warps * 32, 1) k_embedding4(const __grid_
     uint4 stC = load_states(gw, tc), stN = make_uint4(kRansL, kRansL, kRansL, kRansL);
     if (gw < p.total) issue(tc, offC, mlC, 0);
 
-    const uint32_t lut_s = smem_s;
     uint32_t parity0 = 0, parity1 = 0, stage = 0;
     uint32_t s0, s1, s2, s3, pos0, pos1, pos2, pos3;
     auto renorm4 = [&](uint32_t y0, uint32_t y1, uint32_t y2, uint32_t y3) {
@@ -181,17 +183,17 @@ __global__ void __launch_bounds__(kEmb4Warps * 32, 1) k_embedding4(const __grid_
 #pragma unroll 4
                 for (uint32_t i = 0; i < tc.inner; ++i) {        // the rows above the wanted one
                     const uint32_t y0 = lds_u8(pos0), y1 = lds_u8(pos1), y2 = lds_u8(pos2), y3 = lds_u8(pos3);
-                    (void)decode_fast(s0, lut_s);
-                    (void)decode_fast(s1, lut_s);
-                    (void)decode_fast(s2, lut_s);
-                    (void)decode_fast(s3, lut_s);
+                    (void)decode_aligned(s0, lut_s);
+                    (void)decode_aligned(s1, lut_s);
+                    (void)decode_aligned(s2, lut_s);
+                    (void)decode_aligned(s3, lut_s);
                     renorm4(y0, y1, y2, y3);
                 }
             }
             uint32_t w01 = 0, w23 = 0;
             if (ok && tile_live) {
-                const uint32_t e0 = lds_u32(lut_s + ((s0 & kProbMask) << 2)), e1 = lds_u32(lut_s + ((s1 & kProbMask) << 2));
-                const uint32_t e2 = lds_u32(lut_s + ((s2 & kProbMask) << 2)), e3 = lds_u32(lut_s + ((s3 & kProbMask) << 2));
+                const uint32_t e0 = lds_u32(((s0 << 2) & (kProbMask << 2)) | lut_s), e1 = lds_u32(((s1 << 2) & (kProbMask << 2)) | lut_s);
+                const uint32_t e2 = lds_u32(((s2 << 2) & (kProbMask << 2)) | lut_s), e3 = lds_u32(((s3 << 2) & (kProbMask << 2)) | lut_s);
                 const uint32_t a01 = __byte_perm(e0, e1, 0x6521), a23 = __byte_perm(e2, e3, 0x6521);
                 w01 = ((a01 << 3) & 0x7F807F80u) | (__byte_perm(man, 0u, 0x1100) & 0x807F807Fu);
                 w23 = ((a23 << 3) & 0x7F807F80u) | (__byte_perm(man, 0u, 0x3322) & 0x807F807Fu);
@@ -239,7 +241,7 @@ int launch_embedding4(const EmbArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     p.blocks_n = (g.tiles_n + 3) / 4;
     p.total = a.n_ids * p.blocks_n;
     p.out_vec = ((reinterpret_cast<uintptr_t>(a.out) & 7u) == 0 && (a.ldo & 3) == 0) ? 1u : 0u;
-    const uint32_t fixed = kLutBytes + kEmb4BarBytes;
+    const uint32_t fixed = 2 * kLutBytes + kEmb4BarBytes;           // up to one table size is lost to the table's alignment
     const uint32_t warp_bytes = 2 * p.stage_bytes;
     if ((uint32_t)max_smem < fixed + 4 * warp_bytes) return 1;
     uint32_t warps = ((uint32_t)max_smem - fixed) / warp_bytes;
