@@ -53,3 +53,35 @@ def test_random_shapes(K, N, th, M, seed):
     y2 = ci.fused_rans_linear_triton(x.cuda(), weight_shape=(K, N), SPLIT_K=0, **a).double().cpu()
     assert torch.equal(y, y2)                                   # deterministic, workspace left clean
     assert _lib.kernel_status("cuda:0") == 0
+
+
+# Matrices with at least six two-tile units per multiprocessor take the four-streams-per-lane GEMV kernel
+# (smaller ones take the two-streams kernel): every batch size of both of its instantiations (weights as
+# the A operand up to 8 rows, as the B operand for 9..16), a ragged last column tile, a bias, and several
+# warps sharing a column group (partials + ticket).
+@pytest.mark.parametrize("K,N,th", [(1024, 2048, 16), (2048, 1056, 32), (4096, 1000, 64), (8192, 1024, 128)])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 7, 8, 9, 12, 16])
+def test_four_stream_gemv_all_batches(K, N, th, M):
+    import comp_inference_b200 as ci
+    from comp_inference_b200 import _lib
+    W = make_weight(K, N, 7000 + K + N)
+    c = ci.compress_weight_cuda(W.cuda(), th, 32)
+    a = dict(compressed_data=c["rans_exp_stream"], initial_states=c["rans_exp_states"], tables=c["rans_exp_tables"],
+             slot_map=c["rans_exp_slot_map"], tile_offsets=c["rans_exp_tile_offsets"],
+             tile_max_lens=c["rans_exp_tile_max_lens"], tile_k=c["tile_height"], tile_n=c["tile_width"],
+             mantissas=c["rans_man_raw"])
+    g = torch.Generator().manual_seed(M * 31 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    ref = x.double() @ W.double() + bias.double()
+    y = ci.fused_rans_linear_triton(x.cuda(), weight_shape=(K, N), SPLIT_K=0, bias=bias.cuda(), **a).double().cpu()
+    assert y.shape == (M, N)
+    err = float((y - ref).abs().max() / float(ref.abs().max()))
+    assert err <= REL_TOL, err
+    # every row on its own, so that a row landing in another row's place cannot hide in the maximum
+    for m in range(M):
+        e = float((y[m] - ref[m]).abs().max() / float(ref[m].abs().max()))
+        assert e <= 2 * REL_TOL, (m, e)
+    y2 = ci.fused_rans_linear_triton(x.cuda(), weight_shape=(K, N), SPLIT_K=0, bias=bias.cuda(), **a).double().cpu()
+    assert torch.equal(y, y2)
+    assert _lib.kernel_status("cuda:0") == 0
