@@ -8,10 +8,10 @@
 // is exactly the fragment ownership of mma.sync m16n8k16 -- the four threads that share g hold
 // different k -- once the k index of the instruction is read as "segment q, rows r..r+3": four
 // consecutive symbols of a stream are one packed pair of registers, the matching activations
-// x[m][those rows] are one 8-byte load per activation row.  Up to 8 activation rows the weights are the
-// A operand (two columns of the lane = mma rows g and g + 8, two mma per four rows) and activation row g
-// the B operand; for 9..16 rows the weights are the B operand (one mma per column) and activation rows
-// g, g + 8 the A operand.  No shared-memory transpose, no ldmatrix.
+// x[m][those rows] are one 8-byte load per activation row.  The weights are the A operand (two columns
+// of the lane = mma rows g and g + 8, two mma per four rows) and activation row g the B operand; an
+// instantiation for 9..16 activation rows issues a second pair of mma for row g + 8.  No shared-memory
+// transpose, no ldmatrix.
 //
 // Measured on a B200 this kernel is bound neither by HBM (10 %) nor by one on-chip unit alone: issue
 // slots are 41 % busy with about 20 integer-heavy instructions per decoded symbol on half-rate pipes,
@@ -99,12 +99,12 @@ __device__ __forceinline__ void renorm4(uint32_t &s0, uint32_t &s1, uint32_t &s2
 
 // Four symbols of each of the lane's streams -> four packed weight pairs per column -> tensor core.
 // m = sign+mantissa words of the four rows, xf = the activations of those rows.
-//  * WA == false (up to 16 activation rows): the weights are the B operand, one mma per column of the lane
-//    (mma column n = g), the activations of rows g and g + 8 the A operand (xf = a0..a3);
-//  * WA == true (up to 8 activation rows): the weights are the A operand -- columns c and c + 1 of the lane
-//    are mma rows g and g + 8, so one mma takes two columns -- and activation row g is the B operand
-//    (xf[0], xf[1]).  Half the mma instructions, half the activation loads, half the accumulators.
-template <bool WA>
+// The weights are the A operand -- columns c and c + 1 of the lane are mma rows g and g + 8, so one mma takes
+// two columns -- and activation row g is the B operand (xf[0], xf[1]); with more than 8 activation rows (HI)
+// a second pair of mma takes activation row g + 8 (xf[2], xf[3]).  Compared with the weights as the B
+// operand (one mma per column) this halves the mma count and the accumulators for up to 8 rows and needs
+// no interleaving of the activation registers.
+template <bool HI>
 __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_t &s1, uint32_t &s2, uint32_t &s3,
                                        uint32_t &p0, uint32_t &p1, uint32_t &p2, uint32_t &p3, uint32_t lut_s,
                                        const uint32_t (&m)[4], const uint32_t (&xf)[4]) {
@@ -131,20 +131,17 @@ __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_
         b[2][h] = weight_pair4<2>(e2, f2, m[2 * h], m[2 * h + 1]);
         b[3][h] = weight_pair4<3>(e3, f3, m[2 * h], m[2 * h + 1]);
     }
-    if constexpr (WA) {
-        const uint32_t w01[4] = {b[0][0], b[1][0], b[0][1], b[1][1]};
-        const uint32_t w23[4] = {b[2][0], b[3][0], b[2][1], b[3][1]};
-        mma_bf16(acc[0], w01, xf[0], xf[1]);
-        mma_bf16(acc[1], w23, xf[0], xf[1]);
-    } else {
-        mma_bf16(acc[0], xf, b[0][0], b[0][1]);
-        mma_bf16(acc[1], xf, b[1][0], b[1][1]);
-        mma_bf16(acc[2], xf, b[2][0], b[2][1]);
-        mma_bf16(acc[3], xf, b[3][0], b[3][1]);
+    const uint32_t w01[4] = {b[0][0], b[1][0], b[0][1], b[1][1]};
+    const uint32_t w23[4] = {b[2][0], b[3][0], b[2][1], b[3][1]};
+    mma_bf16(acc[0], w01, xf[0], xf[1]);
+    mma_bf16(acc[1], w23, xf[0], xf[1]);
+    if constexpr (HI) {
+        mma_bf16(acc[2], w01, xf[2], xf[3]);
+        mma_bf16(acc[3], w23, xf[2], xf[3]);
     }
 }
 
-template <bool WA>
+template <bool HI>
 __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid_constant__ Mma4Args p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs &a = p.a;
@@ -240,9 +237,8 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
     };
 
-    // Writes the finished (or partial) sums of column group grp.  This lane's accumulators are rows
-    // gq and gq + 8 of the activation batch, columns 8q .. 8q+7 of the group: mma column n of block c is
-    // column 4n + c, and the D fragment holds n = 2q and 2q + 1.
+    // Writes the finished (or partial) sums of column group grp.  After a lane exchange (below) a lane
+    // works on rows gq and gq + 8 of the activation batch, columns 8q .. 8q+7 of the group.
     auto flush = [&](uint32_t grp) {
         const uint32_t first_w = (grp * p.pairs_k) / p.per_warp;
         const uint32_t last_w = ((grp + 1) * p.pairs_k - 1) / p.per_warp;
@@ -272,10 +268,10 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             }
         };
         float v0[8], v1[8];
-        if constexpr (WA) {
-            // The D fragments hold columns 4 gq .. 4 gq + 3 of activation rows 2q and 2q + 1
-            // (acc[c / 2][2 (c % 2) + row parity]); bring them into the layout of the other path -- row gq,
-            // columns 8q .. 8q + 7 -- which everything below works on.  Sources: lanes (2q, gq / 2) and
+        {
+            // The D fragments hold columns 4 gq .. 4 gq + 3 of activation rows 2q and 2q + 1 (acc[c / 2], and
+            // acc[2 + c / 2] for rows 8 + 2q, 9 + 2q; element 2 (c % 2) + row parity).  Everything below works on
+            // "row gq (v0) and gq + 8 (v1), columns 8q .. 8q + 7": fetch those from lanes (2q, gq / 2) and
             // (2q + 1, gq / 2).
             const uint32_t srcA = (2 * q) * 4 + (gq >> 1), srcB = srcA + 4;
             const bool odd = gq & 1;
@@ -287,14 +283,13 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
                 v0[c] = odd ? a1 : a0;
                 v0[4 + c] = odd ? b1 : b0;
                 v1[c] = v1[4 + c] = 0.f;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                v0[j] = acc[j][0];
-                v0[4 + j] = acc[j][1];
-                v1[j] = acc[j][2];
-                v1[4 + j] = acc[j][3];
+                if constexpr (HI) {
+                    const float h0 = acc[2 + (c >> 1)][2 * (c & 1)], h1 = acc[2 + (c >> 1)][2 * (c & 1) + 1];
+                    const float c0 = __shfl_sync(kFull, h0, srcA), c1 = __shfl_sync(kFull, h1, srcA);
+                    const float d0 = __shfl_sync(kFull, h0, srcB), d1 = __shfl_sync(kFull, h1, srcB);
+                    v1[c] = odd ? c1 : c0;
+                    v1[4 + c] = odd ? d1 : d0;
+                }
             }
         }
         if (count == 1) {
@@ -422,15 +417,12 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 #pragma unroll
         for (int i = 0; i < 4; ++i) m[i] = ldg_stream_u32(mp + i * 32);
         const uint2 v0 = __ldg(reinterpret_cast<const uint2 *>(xp0));
-        if constexpr (WA) {
-            xf[0] = v0.x;
-            xf[1] = v0.y;
-            xf[2] = xf[3] = 0;
-        } else {
+        xf[0] = v0.x;
+        xf[1] = v0.y;
+        xf[2] = xf[3] = 0;
+        if constexpr (HI) {
             const uint2 v1 = __ldg(reinterpret_cast<const uint2 *>(xp1));
-            xf[0] = v0.x;
-            xf[1] = v1.x;
-            xf[2] = v0.y;
+            xf[2] = v1.x;
             xf[3] = v1.y;
         }
     };
@@ -497,12 +489,12 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 #pragma unroll 1
         for (uint32_t gi = 0; gi < n_groups; gi += 2) {         // operands are fetched one group ahead
             fetch(mp + 128, xp0 + 4, xp1 + 4, mB, xB);
-            group4<WA>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
+            group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
             mp += 256;
             xp0 += 8;
             xp1 += 8;
             if (gi + 2 < n_groups) fetch(mp, xp0, xp1, mA, xA);
-            group4<WA>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
+            group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
         }
         stage ^= 1;
     }
@@ -578,7 +570,7 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    CI_CUDA(cudaLaunchKernelEx(&cfg, a.M <= 8 ? k_linear_mma4<true> : k_linear_mma4<false>, p));
+    CI_CUDA(cudaLaunchKernelEx(&cfg, a.M <= 8 ? k_linear_mma4<false> : k_linear_mma4<true>, p));
     return CI_OK;
 }
 
