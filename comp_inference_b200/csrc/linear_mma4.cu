@@ -319,13 +319,17 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             *reinterpret_cast<float4 *>(mine + (gq + 8) * 32) = make_float4(v1[0], v1[1], v1[2], v1[3]);
             *reinterpret_cast<float4 *>(mine + (gq + 8) * 32 + 4) = make_float4(v1[4], v1[5], v1[6], v1[7]);
         }
-        __threadfence();
+        // One acquire-release ticket instead of fence + relaxed ticket + fence: the warp barrier orders the
+        // lanes' partial stores before lane 0's release, and the last arriver's acquire before the lanes' loads.
         __syncwarp();
         uint32_t last = 0;
-        if (lane == 0) last = atomicAdd(a.tickets + grp, 1u) == count - 1;
+        if (lane == 0) {
+            uint32_t seen;
+            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.tickets + grp) : "memory");
+            last = seen == count - 1;
+        }
         last = __shfl_sync(kFull, last, 0);
         if (!last) return;
-        __threadfence();
         if (a.M <= 2) {
             // One or two activation rows: lane = column, up to sixteen partials of both rows in flight at
             // once, so the reduction costs one L2 round trip.  Fixed order: partial first_w, first_w + 1, ...
