@@ -201,13 +201,17 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
             if (r0 + 8 < a.M)
                 *reinterpret_cast<float2 *>(mine + (r0 + 8) * 32 + nb * 8 + c0) = make_float2(acc[nb][2], acc[nb][3]);
         }
-        __threadfence();
+        // One acquire-release ticket: the warp barrier orders the lanes' partial stores before lane 0's
+        // release, and the last arriver's acquire before the lanes' loads.
         __syncwarp();
         uint32_t last = 0;
-        if (lane == 0) last = atomicAdd(a.tickets + grp, 1u) == count - 1;
+        if (lane == 0) {
+            uint32_t seen;
+            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.tickets + grp) : "memory");
+            last = seen == count - 1;
+        }
         last = __shfl_sync(kFull, last, 0);
         if (!last) return;
-        __threadfence();
         if (a.M <= 2) {
             // One or two activation rows: lane = column, up to sixteen partials of both rows in flight at
             // once, so the whole reduction of a 4096-row matrix costs one L2 round trip.  Same summation
