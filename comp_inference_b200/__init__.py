@@ -21,14 +21,17 @@ from .ops import (  # noqa: F401
     fused_rans_embedding_triton,
     fused_rans_embedding_triton_uncoalesced,
     fused_rans_linear_transposed_triton,
+    fused_rans_linear_transposed_triton_uncoalesced,
     fused_rans_linear_triton,
     fused_rans_linear_triton_uncoalesced,
+    rans_decomp_triton,
     rans_decomp_triton_tiled,
     rans_decompress_bf16,
     triton_matmul,
 )
 from .rans_saving import (  # noqa: F401
     compress_model,
+    compressed_state_dict,
     load_compressed_model,
     pack_and_save_tensors,
     save_rans_model_package,
@@ -40,8 +43,15 @@ from .pytorch_runtime import (  # noqa: F401
     RansLMHead,
     RansRowParallelLinear,
     RansWorkspace,
+    RansFusedLinear,
+    RansFusedSlice,
+    RansVocabParallelLMHead,
+    close_tensor_parallel,
     load_compressed_model_with_auto_model,
+    patch_model,
     patch_model_tensor_parallel,
+    prepare_model,
 )
+from ._lib import check_status, reserve_workspace, validate_compressed  # noqa: F401
 
 __all__ = [n for n in dir() if not n.startswith("_")]

@@ -43,6 +43,10 @@ SIGNATURES = {
     "ci_abi_version": (C.c_int, []),
     "ci_last_error": (C.c_char_p, []),
     "ci_device_info": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ci_workspace_status_word": (C.c_void_p, [_V]),
+    "ci_status": (C.c_int, [_V, u32p, C.c_int, _S]),
+    "ci_validate_tiled_metadata": (C.c_int, [_V, _V, _V, _V, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32,
+                                             C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "ci_build_tables": (C.c_int, [_V, _V, _V, _V]),
     "ci_prepare_lut": (C.c_int, [_V, _V, _V, _S]),
     "ci_split_bf16": (C.c_int, [_V, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _V, _V, _V, _V, _S]),
@@ -66,20 +70,30 @@ SIGNATURES = {
                             C.c_uint32, _S]),
     "ci_linear_static_max_bytes": (C.c_size_t, []),
     "ci_linear_static": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _S]),
+    "ci_linear_static_status": (C.c_int, [u32p, C.c_int, _S]),
     "ci_linear_transposed": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V,
                                        C.c_size_t, _S]),
     "ci_embedding": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_uint64, _V, C.c_int64, _S]),
     "ci_linear_dense": (C.c_int, [C.POINTER(DenseWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V,
                                   C.c_size_t, C.c_uint32, _S]),
     "ci_embedding_dense": (C.c_int, [C.POINTER(DenseWeight), _V, C.c_uint64, _V, C.c_int64, _S]),
+    "ci_linear_transposed_dense": (C.c_int, [C.POINTER(DenseWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V,
+                                             C.c_size_t, _S]),
     "ci_decode_legacy": (C.c_int, [_V, C.c_uint64, _V, _V, C.c_uint32, C.c_uint64, _V, _V, _V, _S]),
     "ci_encode_legacy_sizes": (C.c_int, [_V, C.c_uint64, C.c_uint32, _V, _V, _V, _V, _S]),
     "ci_encode_legacy_write": (C.c_int, [_V, C.c_uint64, C.c_uint32, _V, _V, _V, C.c_uint64, _S]),
+    "ci_decode_legacy_segments": (C.c_int, [_V, C.c_uint64, _V, _V, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _V,
+                                            _V, _V, _S]),
+    "ci_encode_legacy_segments_sizes": (C.c_int, [_V, C.c_uint32, C.c_uint32, C.c_uint32, _V, _V, _V, _V, _S]),
+    "ci_encode_legacy_segments_write": (C.c_int, [_V, C.c_uint32, C.c_uint32, C.c_uint32, _V, _V, _V, C.c_uint64, _S]),
     "ci_allreduce_buffer_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
     "ci_allreduce_counter_bytes": (C.c_size_t, []),
     "ci_linear_allreduce_counter_bytes": (C.c_size_t, []),
+    "ci_linear_allreduce_qualifies": (C.c_int, [C.POINTER(TiledWeight), C.c_uint32]),
+    "ci_allreduce_set_poll_limit": (None, [C.c_uint32]),
     "ci_linear_allreduce": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, _V, C.c_size_t, _V,
                                       C.c_uint32, _V, C.c_uint32, C.c_uint32, _V, _S]),
+    "ci_allgather_oneshot": (C.c_int, [_V, _V, C.c_uint32, C.c_uint32, C.c_uint32, _V, _V, C.c_uint32, C.c_uint32, _V, _S]),
     "ci_allreduce_oneshot": (C.c_int, [_V, _V, C.c_uint32, C.c_uint32, _V, _V, C.c_uint32, C.c_uint32, _V, _S]),
 }
 
@@ -176,23 +190,89 @@ def max_tile_len(tile_max_lens):
     return v
 
 
-# ---- split-K workspace: one zero-initialised buffer per device, grown on demand
+# ---- split-K / stream-K workspaces ---------------------------------------------------------
+# One zero-initialised buffer per (device, CUDA stream): kernels of one stream run in order and leave the
+# ticket counters zeroed, so they can share; two streams may overlap on the GPU and must not (the
+# reference keeps one global buffer for every layer and stream, comp_inference/pytorch_runtime.py:386-394).
+# A buffer that was handed out is never freed: a CUDA graph captured earlier keeps replaying into the
+# address it saw, so when a larger one is needed the old tensor is retired, not dropped.
 _workspaces = {}
+_retired = []
+_MIN_WORKSPACE = 8 << 20
 
 
 def workspace(device, nbytes):
-    ws = _workspaces.get(device)
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[device] = ws
+        if ws is not None:
+            _retired.append((key[0], ws))
+        ws = torch.zeros(max(int(nbytes), _MIN_WORKSPACE), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
     return ws
 
 
+def reserve_workspace(device, nbytes):
+    """Sizes the current stream's workspace up front (e.g. for the largest M x N a model will see) so that
+    no later call has to replace it."""
+    return workspace(device, nbytes)
+
+
+def _status_words(device):
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    bufs = [ws for (dev, _), ws in _workspaces.items() if dev == device]
+    bufs += [ws for dev, ws in _retired if dev == device]
+    return bufs
+
+
 def kernel_status(device):
-    """Status word the staged kernels set when a bounded wait ran out or metadata was inconsistent
-    (0 = fine).  Reading it synchronises with the device."""
-    ws = _workspaces.get(torch.device(device))
-    return 0 if ws is None else int(ws[4095 * 4:4096 * 4].view(torch.int32).item())
+    """First non-zero status word among this device's workspaces (0 = fine): set by the staged kernels when a
+    bounded wait ran out or tile metadata contradicted the descriptor.  Reading it synchronises with the device."""
+    for ws in _status_words(device):
+        v = int(ws[4095 * 4:4096 * 4].view(torch.int32).item())
+        if v:
+            return v
+    return 0
+
+
+def check_status(device=None, clear=True):
+    """Raises RuntimeError (CI_E_DEVICE) if any kernel that used one of this device's workspaces reported an
+    error through its status word; call it wherever the host waits for results anyway.  Goes through the C ABI
+    (ci_status), which waits for the current stream."""
+    lib = load()
+    device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    for ws in _status_words(device):
+        word = lib.ci_workspace_status_word(ptr(ws))
+        check(lib.ci_status(C.c_void_p(word), None, 1 if clear else 0, stream()))
+
+
+def validate_compressed(c, K=None, N=None, th=None, tw=None, max_tile_len=0):
+    """ci_validate_tiled_metadata on a dict of package tensors (any device; copied to the host here).
+    Raises RuntimeError naming the first inconsistent entry."""
+    import numpy as np
+    if K is None:
+        K, N = c["shape"]
+        th, tw = c["tile_height"], c["tile_width"]
+    host = lambda t, dt: np.ascontiguousarray(t.detach().cpu().contiguous().view(dt).numpy())
+    off = host(c["rans_exp_tile_offsets"], torch.int32).view(np.uint32)
+    lens = host(c["rans_exp_tile_max_lens"], torch.int32).view(np.uint32)
+    tables = host(c["rans_exp_tables"], torch.int32).view(np.uint32) if "rans_exp_tables" in c else None
+    slot = host(c["rans_exp_slot_map"], torch.uint8) if "rans_exp_slot_map" in c else None
+    tiles = -(-int(K) // int(th)) * -(-int(N) // int(tw))
+    if off.size != tiles or lens.size != tiles:
+        raise RuntimeError(f"comp_inference_b200: tile_offsets / tile_max_lens have {off.size} / {lens.size} "
+                           f"entries, {tiles} expected (code -1)")
+    man = c.get("rans_man_raw")
+    check(load().ci_validate_tiled_metadata(
+        off.ctypes.data, lens.ctypes.data, tables.ctypes.data if tables is not None else None,
+        slot.ctypes.data if slot is not None else None, int(c["rans_exp_stream"].numel()),
+        int(c["rans_exp_states"].numel()), int(man.numel()) if man is not None else 0, int(K), int(N), int(th),
+        int(tw), int(max_tile_len)))
 
 
 def tiled_weight(stream_t, states, tables, slot_map, tile_offsets, tile_max_lens, mantissa, K, N, th, tw, lut=None,

@@ -221,7 +221,38 @@ def _legacy_decompress(self, stream, states, sizes, num_streams, output_len, fre
     return out, ms
 
 
+def _legacy_compress_segments(self, data, freqs, cdf, seg_rows=512):
+    """The legacy layout with the stream assignment of the reference's own legacy encoder
+    (src/cuda/rans_kernels.cuh:393-509): stream seg * width + col codes rows [seg * seg_rows, + seg_rows) of
+    column col of a 2-D uint8 tensor; this is what ``rans_decomp_triton`` (comp_inference/rans_triton.py:243-271,
+    fixed seg_rows = 512) decodes.  Same result type as ``compress``."""
+    dev = _device()
+    t = torch.from_numpy(np.ascontiguousarray(data)) if isinstance(data, np.ndarray) else data
+    if t.dtype != torch.uint8 or t.dim() != 2 or t.numel() == 0:
+        raise RuntimeError("expected a non-empty 2-D uint8 tensor")
+    rows, cols = int(t.shape[0]), int(t.shape[1])
+    f = _as_u16_host(freqs, "freqs")
+    c = _as_u16_host(cdf, "cdf")
+    S = -(-rows // int(seg_rows)) * cols
+    plane = t.to(dev).contiguous()
+    states = torch.empty(S, dtype=torch.uint32, device=dev)
+    sizes = torch.empty(S, dtype=torch.uint32, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.ci_encode_legacy_segments_sizes(_lib.ptr(plane), rows, cols, int(seg_rows), f.ctypes.data,
+                                                   c.ctypes.data, _lib.ptr(states), _lib.ptr(sizes), _lib.stream()))
+    max_len = int(sizes.view(torch.int32).max().item())
+    stream = torch.empty(max_len * S, dtype=torch.uint8, device=dev)
+    _lib.check(lib.ci_encode_legacy_segments_write(_lib.ptr(plane), rows, cols, int(seg_rows), f.ctypes.data,
+                                                   c.ctypes.data, _lib.ptr(stream), stream.numel(), _lib.stream()))
+    tables, slot_map = _tables_host(f, c)
+    return TensorCompressResult(success=True, stream=stream.cpu(), states=states.cpu().view(torch.int32),
+                                sizes=sizes.cpu().view(torch.int32), tables=tables, slot_map=slot_map,
+                                checkpoints=torch.empty(0, dtype=torch.uint64), num_streams=S,
+                                stream_len=int(stream.numel()))
+
+
 RansManager.compress = _legacy_compress
+RansManager.compress_segments = _legacy_compress_segments
 RansManager.decompress = _legacy_decompress
 RansManager.decompress_into = _legacy_decompress_into
 

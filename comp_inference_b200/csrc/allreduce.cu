@@ -31,6 +31,8 @@ struct ArArgs {
     const uint16_t *in;
     uint16_t *out;
     uint32_t n, capacity, rank, world;
+    uint32_t polls;                    // loads of one slot before a wait gives up
+    uint32_t gather_cols;              // 0: sum over the ranks; else all-gather of [n / gather_cols, gather_cols] blocks
 };
 
 __device__ __forceinline__ void st_pair(uint2 *p, uint32_t data, uint32_t tag) {
@@ -56,15 +58,26 @@ __global__ void __launch_bounds__(kArThreads) k_allreduce_oneshot(const __grid_c
         for (uint32_t q = 0; q < a.world; ++q) st_pair(reinterpret_cast<uint2 *>(a.bufs[q]) + my_slot + i, data, seq);
         float s0 = 0.f, s1 = 0.f;
         const uint2 *mine = reinterpret_cast<const uint2 *>(a.bufs[a.rank]) + (size_t)parity * a.world * cap2 + i;
+        // all-gather: element e = (row, col) of rank q's block lands at out[row][q * gather_cols + col];
+        // gather_cols is even, so a pair never straddles two rows
+        const uint32_t g_row = a.gather_cols ? (2 * i) / a.gather_cols : 0u;
+        const uint32_t g_col = a.gather_cols ? (2 * i) - g_row * a.gather_cols : 0u;
         for (uint32_t q = 0; q < a.world; ++q) {
             uint2 v = ld_pair(mine + (size_t)q * cap2);
-            for (uint32_t it = 0; v.y != seq && it < kArPolls; ++it) v = ld_pair(mine + (size_t)q * cap2);
+            for (uint32_t it = 0; v.y != seq && it < a.polls; ++it) v = ld_pair(mine + (size_t)q * cap2);
             timed_out |= v.y != seq;
-            s0 += bf16_bits_to_float(v.x & 0xFFFFu);
-            s1 += bf16_bits_to_float(v.x >> 16);
+            if (a.gather_cols) {
+                uint32_t *dst = reinterpret_cast<uint32_t *>(a.out + ((size_t)g_row * a.world + q) * a.gather_cols + g_col);
+                *dst = v.x;
+            } else {
+                s0 += bf16_bits_to_float(v.x & 0xFFFFu);
+                s1 += bf16_bits_to_float(v.x >> 16);
+            }
         }
-        a.out[2 * i] = float_to_bf16_bits(s0);
-        if (2 * i + 1 < a.n) a.out[2 * i + 1] = float_to_bf16_bits(s1);
+        if (a.gather_cols == 0) {
+            a.out[2 * i] = float_to_bf16_bits(s0);
+            if (2 * i + 1 < a.n) a.out[2 * i + 1] = float_to_bf16_bits(s1);
+        }
     }
     if (timed_out && a.status) atomicExch(a.status, 9u);
     __syncthreads();
@@ -75,7 +88,11 @@ __global__ void __launch_bounds__(kArThreads) k_allreduce_oneshot(const __grid_c
 
 using namespace ci;
 
+static uint32_t g_ar_polls = kArPolls;
+
 extern "C" {
+
+void ci_allreduce_set_poll_limit(uint32_t polls) { g_ar_polls = polls ? polls : kArPolls; }
 
 size_t ci_allreduce_buffer_bytes(uint32_t world, uint32_t capacity) {
     return (size_t)2 * world * (capacity / 2) * 8;             // two parities x world slots x pairs of (data, tag)
@@ -96,6 +113,41 @@ int ci_allreduce_oneshot(const uint16_t *d_in, uint16_t *d_out, uint32_t n, uint
     }
     a.counters = d_counters; a.status = d_status; a.in = d_in; a.out = d_out;
     a.n = n; a.capacity = capacity; a.rank = rank; a.world = world;
+    a.polls = g_ar_polls;
+    a.gather_cols = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kArCtas);
+    cfg.blockDim = dim3(kArThreads);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    CI_CUDA(cudaLaunchKernelEx(&cfg, k_allreduce_oneshot, a));
+    return CI_OK;
+}
+
+int ci_allgather_oneshot(const uint16_t *d_in, uint16_t *d_out, uint32_t rows, uint32_t cols, uint32_t capacity,
+                         void *const *peer_bufs, uint32_t *d_counters, uint32_t rank, uint32_t world, uint32_t *d_status,
+                         ci_stream_t stream) {
+    CI_REQUIRE(d_in && d_out && peer_bufs && d_counters, "null pointer");
+    CI_REQUIRE(d_in != d_out, "the all-gather cannot run in place");
+    CI_REQUIRE(capacity % 8 == 0, "capacity must be a multiple of 8 elements");
+    CI_REQUIRE(world >= 1 && world <= kArMaxWorld && rank < world, "world size %u / rank %u out of range", world, rank);
+    CI_REQUIRE(cols % 2 == 0 && cols > 0, "the per-rank width %u must be even", cols);
+    CI_REQUIRE((uint64_t)rows * cols <= capacity, "%u x %u elements exceed the buffer capacity %u", rows, cols, capacity);
+    CI_REQUIRE((reinterpret_cast<uintptr_t>(d_out) & 3u) == 0, "output must be 4-byte aligned");
+    if (rows == 0) return CI_OK;
+    ArArgs a;
+    for (uint32_t q = 0; q < kArMaxWorld; ++q) {
+        a.bufs[q] = q < world ? reinterpret_cast<uint16_t *>(peer_bufs[q]) : nullptr;
+        CI_REQUIRE(q >= world || a.bufs[q], "null peer pointer for rank %u", q);
+    }
+    a.counters = d_counters; a.status = d_status; a.in = d_in; a.out = d_out;
+    a.n = rows * cols; a.capacity = capacity; a.rank = rank; a.world = world;
+    a.polls = g_ar_polls;
+    a.gather_cols = cols;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kArCtas);
     cfg.blockDim = dim3(kArThreads);

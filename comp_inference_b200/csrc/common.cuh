@@ -38,6 +38,13 @@ int cuda_fail(cudaError_t e, const char *what);
 
 int sm_count();
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a device's context, not to the process: a
+// launcher keeps one SmemLimit per kernel and raises the limit once on every device it runs on.
+struct SmemLimit {
+    size_t granted[64];
+};
+int ensure_smem_limit(SmemLimit &st, const void *kernel, size_t bytes);
+
 // ---- geometry ---------------------------------------------------------------
 struct Geom {
     uint32_t K, N, th, tw;

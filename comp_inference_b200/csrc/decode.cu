@@ -170,13 +170,17 @@ __global__ void __launch_bounds__(256) k_decode_dense(DenseArgs a, void *out) {
     }
 }
 
-// Legacy flat layout (src/cuda/rans_kernels.cuh:626-708).
+// Legacy flat layout.  seg_rows == 0: stream g yields flat indices g, g + num_streams, ...
+// (src/cuda/rans_kernels.cuh:626-708).  seg_rows > 0: stream g yields rows [seg * seg_rows, +seg_rows) of
+// column g % cols, seg = g / cols, of a row-major [rows, cols] plane with rows * cols = output_len
+// (comp_inference/rans_triton.py:171-233, the order the reference's legacy encoder writes,
+// src/cuda/rans_kernels.cuh:393-509).
 __global__ void __launch_bounds__(256) k_decode_legacy(const uint8_t *__restrict__ stream,
                                                        const uint32_t *__restrict__ states,
                                                        const uint32_t *__restrict__ sizes, uint32_t num_streams,
                                                        uint64_t output_len, const uint32_t *__restrict__ tables,
                                                        const uint8_t *__restrict__ slot_map,
-                                                       uint8_t *__restrict__ out) {
+                                                       uint8_t *__restrict__ out, uint32_t cols, uint32_t seg_rows) {
     __shared__ uint32_t s_lut[kProbScale];
     load_lut(s_lut, nullptr, tables, slot_map);
     __syncthreads();
@@ -187,6 +191,19 @@ __global__ void __launch_bounds__(256) k_decode_legacy(const uint8_t *__restrict
     c.base = stream;
     c.row = -1;
     if (live) { state = states[gid]; c.base = stream + gid; c.row = (int32_t)sizes[gid] - 1; }
+    if (seg_rows != 0) {
+        const uint64_t col = gid % cols, row0 = (uint64_t)(gid / cols) * seg_rows, rows = output_len / cols;
+        const uint64_t n = (live && row0 < rows) ? (rows - row0 < seg_rows ? rows - row0 : seg_rows) : 0;
+        // every lane walks the warp's longest run: renorm_gmem votes warp-wide
+        const uint64_t n_warp = __reduce_max_sync(kFull, (uint32_t)n);
+        for (uint64_t i = 0; i < n_warp; ++i) {
+            uint32_t e = decode_symbol(state, s_lut);
+            if (i >= n) c.row = -1;
+            renorm_gmem(state, c, num_streams);
+            if (i < n) out[(row0 + i) * cols + col] = (uint8_t)lut_sym(e);
+        }
+        return;
+    }
     uint64_t per_stream = (output_len + num_streams - 1) / num_streams;
     for (uint64_t i = 0; i < per_stream; ++i) {
         uint32_t e = decode_symbol(state, s_lut);
@@ -217,11 +234,8 @@ static int decode_tiled(const ci_tiled_weight *w, void *d_out, cudaStream_t s) {
     if (rc <= 0) return rc;
     uint32_t n_tasks = a.g.tiles_k * a.g.groups;
     size_t smem = kProbScale * 4 + (size_t)kDecWarps * kStageBytes;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[BF16]) {
-        CI_CUDA(cudaFuncSetAttribute(k_decode_tiled<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[BF16] = true;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_decode_tiled<BF16>, smem)) return rc;
     uint32_t blocks = (n_tasks + kDecWarps - 1) / kDecWarps;
     uint32_t cap = (uint32_t)sm_count() * 4;
     if (blocks > cap) blocks = cap;
@@ -274,7 +288,22 @@ int ci_decode_legacy(const uint8_t *d_stream, uint64_t stream_len, const uint32_
     CI_REQUIRE(d_states && d_sizes && d_tables && d_slot_map && d_out, "null pointer");
     CI_REQUIRE(num_streams > 0, "no streams");
     k_decode_legacy<<<(num_streams + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
-        d_stream, d_states, d_sizes, num_streams, output_len, d_tables, d_slot_map, d_out);
+        d_stream, d_states, d_sizes, num_streams, output_len, d_tables, d_slot_map, d_out, 1, 0);
+    CI_LAUNCH_CHECK(k_decode_legacy);
+    return CI_OK;
+}
+
+int ci_decode_legacy_segments(const uint8_t *d_stream, uint64_t stream_len, const uint32_t *d_states,
+                              const uint32_t *d_sizes, uint32_t num_streams, uint32_t rows, uint32_t cols,
+                              uint32_t seg_rows, const uint32_t *d_tables, const uint8_t *d_slot_map, uint8_t *d_out,
+                              ci_stream_t stream) {
+    (void)stream_len;
+    CI_REQUIRE(d_states && d_sizes && d_tables && d_slot_map && d_out, "null pointer");
+    CI_REQUIRE(rows > 0 && cols > 0 && seg_rows > 0, "empty plane or zero segment height");
+    CI_REQUIRE((uint64_t)num_streams == (uint64_t)((rows + seg_rows - 1) / seg_rows) * cols,
+               "%u streams, ceil(%u / %u) * %u expected", num_streams, rows, seg_rows, cols);
+    k_decode_legacy<<<(num_streams + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        d_stream, d_states, d_sizes, num_streams, (uint64_t)rows * cols, d_tables, d_slot_map, d_out, cols, seg_rows);
     CI_LAUNCH_CHECK(k_decode_legacy);
     return CI_OK;
 }

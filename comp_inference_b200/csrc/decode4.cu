@@ -255,11 +255,8 @@ __global__ void __launch_bounds__(kDec4Warps * 32, 1) k_decode4(const __grid_con
 template <bool BF16>
 static int launch_dec4(const Dec4Args &p, uint32_t blocks, uint32_t warps, size_t smem, int max_smem, void *out,
                        cudaStream_t s) {
-    static bool attr = false;
-    if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_decode4<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr = true;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_decode4<BF16>, (size_t)max_smem)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks);
     cfg.blockDim = dim3(warps * 32);

@@ -150,11 +150,8 @@ __global__ void __launch_bounds__(512, 1) k_decode_staged(const __grid_constant_
 template <uint32_t TW, bool BF16>
 static int launch_tw(const StagedDecArgs &p, uint32_t blocks, uint32_t warps, size_t smem, int max_smem, void *out,
                      cudaStream_t s) {
-    static bool attr = false;
-    if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_decode_staged<TW, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr = true;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_decode_staged<TW, BF16>, (size_t)max_smem)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks);
     cfg.blockDim = dim3(warps * 32);

@@ -249,11 +249,8 @@ int launch_embedding4(const EmbArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     uint64_t blocks = (p.total + warps - 1) / warps;
     const uint64_t P = (uint64_t)sm_count();
     if (blocks > P) blocks = P;
-    static bool attr = false;
-    if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_embedding4, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr = true;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_embedding4, (size_t)max_smem)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)blocks);
     cfg.blockDim = dim3(warps * 32);

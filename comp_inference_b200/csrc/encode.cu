@@ -205,17 +205,22 @@ static int encode_write(const uint8_t *d_plane, uint32_t K, uint32_t N, const ui
 // g + num_streams, ... encoded last first; byte b of a stream is stored at stream + g + b * num_streams, so
 // the decoder, which starts at byte sizes[g] - 1, meets them in reverse order of emission.
 // stream == nullptr: count only.
+// seg_rows > 0 selects the reference encoder's own assignment instead (src/cuda/rans_kernels.cuh:393-509):
+// stream g codes rows [seg * seg_rows, + seg_rows) of column g % cols, seg = g / cols.
 __global__ void __launch_bounds__(128) k_encode_legacy(const uint8_t *__restrict__ data, uint64_t n, uint32_t num_streams,
                                                        const uint32_t *__restrict__ info, uint32_t *__restrict__ states,
-                                                       uint32_t *__restrict__ sizes, uint8_t *__restrict__ stream) {
+                                                       uint32_t *__restrict__ sizes, uint8_t *__restrict__ stream,
+                                                       uint32_t cols, uint32_t seg_rows) {
     __shared__ uint32_t s_info[256];
     load_sym_info(s_info, info);
     const uint32_t g = blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= num_streams) return;
-    const uint64_t per_stream = (n + num_streams - 1) / num_streams;
+    const uint64_t per_stream = seg_rows ? seg_rows : (n + num_streams - 1) / num_streams;
+    const uint64_t seg_base = seg_rows ? (uint64_t)(g / cols) * seg_rows * cols + g % cols : g;
+    const uint64_t step = seg_rows ? cols : num_streams;
     uint32_t state = kRansL, cnt = 0;
     for (uint64_t i = per_stream; i-- > 0;) {
-        const uint64_t o = (uint64_t)g + i * num_streams;
+        const uint64_t o = seg_base + i * step;
         if (o >= n) continue;
         const uint32_t inf = s_info[data[o]];
         const uint32_t freq = inf & 0xFFFFu, start = inf >> 16;
@@ -238,22 +243,24 @@ using namespace ci;
 
 extern "C" {
 
-int ci_encode_legacy_sizes(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
-                           const uint16_t *cdf, uint32_t *d_states, uint32_t *d_sizes, ci_stream_t stream) {
+static int legacy_sizes(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                        const uint16_t *cdf, uint32_t *d_states, uint32_t *d_sizes, uint32_t cols, uint32_t seg_rows,
+                        ci_stream_t stream) {
     CI_REQUIRE(d_data && d_states && d_sizes && freqs && cdf, "null pointer");
     CI_REQUIRE(num_streams > 0 && n > 0, "empty input");
     cudaStream_t s = (cudaStream_t)stream;
     uint32_t *d_info = nullptr;
     int rc = upload_sym_info(freqs, cdf, &d_info, s);
     if (rc) return rc;
-    k_encode_legacy<<<(num_streams + 127) / 128, 128, 0, s>>>(d_data, n, num_streams, d_info, d_states, d_sizes, nullptr);
+    k_encode_legacy<<<(num_streams + 127) / 128, 128, 0, s>>>(d_data, n, num_streams, d_info, d_states, d_sizes, nullptr, cols, seg_rows);
     CI_LAUNCH_CHECK(k_encode_legacy);
     CI_CUDA(cudaFreeAsync(d_info, s));
     return CI_OK;
 }
 
-int ci_encode_legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
-                           const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len, ci_stream_t stream) {
+static int legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                        const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len, uint32_t cols, uint32_t seg_rows,
+                        ci_stream_t stream) {
     CI_REQUIRE(d_data && freqs && cdf, "null pointer");
     CI_REQUIRE(d_stream || stream_len == 0, "null stream buffer");
     CI_REQUIRE(num_streams > 0 && n > 0, "empty input");
@@ -263,10 +270,33 @@ int ci_encode_legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_strea
     int rc = upload_sym_info(freqs, cdf, &d_info, s);
     if (rc) return rc;
     CI_CUDA(cudaMemsetAsync(d_stream, 0, stream_len, s));
-    k_encode_legacy<<<(num_streams + 127) / 128, 128, 0, s>>>(d_data, n, num_streams, d_info, nullptr, nullptr, d_stream);
+    k_encode_legacy<<<(num_streams + 127) / 128, 128, 0, s>>>(d_data, n, num_streams, d_info, nullptr, nullptr, d_stream, cols, seg_rows);
     CI_LAUNCH_CHECK(k_encode_legacy);
     CI_CUDA(cudaFreeAsync(d_info, s));
     return CI_OK;
+}
+
+int ci_encode_legacy_sizes(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                           const uint16_t *cdf, uint32_t *d_states, uint32_t *d_sizes, ci_stream_t stream) {
+    return legacy_sizes(d_data, n, num_streams, freqs, cdf, d_states, d_sizes, 1, 0, stream);
+}
+int ci_encode_legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
+                           const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len, ci_stream_t stream) {
+    return legacy_write(d_data, n, num_streams, freqs, cdf, d_stream, stream_len, 1, 0, stream);
+}
+int ci_encode_legacy_segments_sizes(const uint8_t *d_data, uint32_t rows, uint32_t cols, uint32_t seg_rows,
+                                    const uint16_t *freqs, const uint16_t *cdf, uint32_t *d_states, uint32_t *d_sizes,
+                                    ci_stream_t stream) {
+    CI_REQUIRE(rows > 0 && cols > 0 && seg_rows > 0, "empty plane or zero segment height");
+    return legacy_sizes(d_data, (uint64_t)rows * cols, ((rows + seg_rows - 1) / seg_rows) * cols, freqs, cdf, d_states,
+                        d_sizes, cols, seg_rows, stream);
+}
+int ci_encode_legacy_segments_write(const uint8_t *d_data, uint32_t rows, uint32_t cols, uint32_t seg_rows,
+                                    const uint16_t *freqs, const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len,
+                                    ci_stream_t stream) {
+    CI_REQUIRE(rows > 0 && cols > 0 && seg_rows > 0, "empty plane or zero segment height");
+    return legacy_write(d_data, (uint64_t)rows * cols, ((rows + seg_rows - 1) / seg_rows) * cols, freqs, cdf, d_stream,
+                        stream_len, cols, seg_rows, stream);
 }
 
 int ci_encode_tiled_sizes(const uint8_t *d_plane, uint32_t K, uint32_t N, const uint16_t *freqs, const uint16_t *cdf,

@@ -540,11 +540,8 @@ int launch_linear_gemm(const LinArgs &a, uint32_t max_tile_len, size_t partial_c
         set_error("cuTensorMapEncodeTiled failed with code %d", (int)r);
         return CI_E_CUDA;
     }
-    static bool attr = false;
-    if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_linear_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr = true;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_linear_gemm, (size_t)max_smem)) return rc;
     cudaLaunchAttribute pdl[1];
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl[0].val.programmaticStreamSerializationAllowed = 1;

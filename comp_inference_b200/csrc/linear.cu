@@ -261,6 +261,108 @@ __global__ void __launch_bounds__(kLinWarps * 32) k_linear_transposed(LinArgs a,
     }
 }
 
+// Dense-layout LM head (comp_inference/transposed_linear_triton.py:660-810): W stored [K = V rows, N = H
+// columns], one stream per tile column over the whole tile height.  Same scheme as k_linear_transposed:
+// a lane walks the vocabulary rows of its hidden column, 32 rows at a time are summed over the lanes
+// with the shuffle transpose, per-warp row accumulators live in shared memory.
+template <int MT>
+__global__ void __launch_bounds__(kLinWarps * 32) k_linear_transposed_dense(LinArgs a, uint32_t groups_per_split) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint32_t *s_lut = reinterpret_cast<uint32_t *>(smem);
+    const uint32_t warp = threadIdx.x / 32, lane = lane_id();
+    float *s_acc_all = reinterpret_cast<float *>(smem + kProbScale * 4);                  // [warps][th][MT]
+    float *s_acc = s_acc_all + (size_t)warp * a.g.th * MT;
+    __shared__ uint32_t s_flag;
+
+    load_lut(s_lut, a.lut, a.tables, a.slot_map);
+    __syncthreads();
+
+    const uint32_t items = a.g.tiles_k * a.splits;
+    for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+        const uint32_t tk = item % a.g.tiles_k, split = item / a.g.tiles_k;
+        const uint32_t g_begin = split * groups_per_split, g_end = min(g_begin + groups_per_split, a.g.groups);
+        const uint32_t row0 = tk * a.g.th, rows = min(a.g.th, a.g.K - row0);
+        for (uint32_t i = lane; i < a.g.th * MT; i += 32) s_acc[i] = 0.f;
+        __syncwarp();
+
+        for (uint32_t grp = g_begin + warp; grp < g_end; grp += kLinWarps) {
+            const uint32_t n = grp * 32 + lane;
+            const bool live = n < a.g.N;
+            uint32_t tn = n / a.g.tw;
+            if (tn >= a.g.tiles_n) tn = a.g.tiles_n - 1;
+            const uint32_t lc = n % a.g.tw;
+            const size_t t = (size_t)tk * a.g.tiles_n + tn, sid = t * a.g.tw + lc;
+            uint32_t state = kRansL;
+            GmemCursor c;
+            c.base = a.stream;
+            c.row = -1;
+            if (live) { state = a.states[sid]; c.base = a.stream + a.dense_offsets[sid]; c.row = (int32_t)a.dense_sizes[sid] - 1; }
+            const uint8_t *man = a.mantissa + t * a.g.th * a.g.tw + lc;
+            float xv[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) xv[m] = (live && m < (int)a.M) ? load_bf16(a.x + (size_t)m * a.ldx + n) : 0.f;
+            for (uint32_t c0 = 0; c0 < rows; c0 += 32) {
+                float wv[32];
+#pragma unroll
+                for (int r = 0; r < 32; ++r) {
+                    wv[r] = 0.f;
+                    if (c0 + r < rows) {
+                        uint32_t e = decode_symbol(state, s_lut);
+                        renorm_gmem(state, c, 1);
+                        wv[r] = bf16_bits_to_float(assemble_bf16(lut_sym(e), __ldg(man + (size_t)(c0 + r) * a.g.tw)));
+                    }
+                }
+                const uint32_t i = c0 + lane;                   // after the transpose lane r holds row c0 + r
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float p[32];
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) p[r] = wv[r] * xv[m];
+#pragma unroll
+                    for (int s = 16; s >= 1; s >>= 1) {
+#pragma unroll
+                        for (int j = 0; j < s; ++j) {
+                            bool up = (lane & s) != 0;
+                            float send = up ? p[j] : p[j + s], keep = up ? p[j + s] : p[j];
+                            p[j] = keep + __shfl_xor_sync(kFull, send, s);
+                        }
+                    }
+                    if (i < rows) s_acc[(size_t)i * MT + m] += p[0];
+                }
+                __syncwarp();
+            }
+        }
+
+        __syncthreads();
+        for (uint32_t idx = threadIdx.x; idx < rows * a.M; idx += blockDim.x) {
+            uint32_t r = idx / a.M, m = idx % a.M;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kLinWarps; ++w) v += s_acc_all[((size_t)w * a.g.th + r) * MT + m];
+            uint32_t vrow = row0 + r;
+            if (a.splits == 1) {
+                if (a.bias) v += load_bf16(a.bias + vrow);
+                a.y[(size_t)m * a.ldy + vrow] = float_to_bf16_bits(v);
+            } else {
+                a.partial[((size_t)split * a.M + m) * a.g.K + vrow] = v;
+            }
+        }
+        if (a.splits > 1) {
+            if (last_arrival(a.tickets + tk, a.splits, &s_flag)) {
+                for (uint32_t idx = threadIdx.x; idx < rows * a.M; idx += blockDim.x) {
+                    uint32_t r = idx / a.M, m = idx % a.M, vrow = row0 + r;
+                    float v = 0.f;
+                    for (uint32_t s = 0; s < a.splits; ++s) v += __ldcg(a.partial + ((size_t)s * a.M + m) * a.g.K + vrow);
+                    if (a.bias) v += load_bf16(a.bias + vrow);
+                    a.y[(size_t)m * a.ldy + vrow] = float_to_bf16_bits(v);
+                }
+                if (threadIdx.x == 0) a.tickets[tk] = 0;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // -------------------------------------------------------------------- host ---
 
 static LinArgs base_args(const ci_tiled_weight *w) {
@@ -286,11 +388,8 @@ static size_t workspace_bytes(uint32_t M, uint32_t n_out) {
 template <int MT>
 static int launch_linear(LinArgs a, cudaStream_t s) {
     size_t smem = kProbScale * 4 + (size_t)kLinWarps * kLinStage;
-    static bool attr = false;
-    if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_linear<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr = true;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_linear<MT>, smem)) return rc;
     uint32_t items = a.g.groups * a.splits, cap = (uint32_t)sm_count() * 4;
     k_linear<MT><<<items < cap ? items : cap, kLinWarps * 32, smem, s>>>(a);
     CI_LAUNCH_CHECK(k_linear);
@@ -300,14 +399,22 @@ static int launch_linear(LinArgs a, cudaStream_t s) {
 template <int MT>
 static int launch_transposed(LinArgs a, uint32_t groups_per_split, cudaStream_t s) {
     size_t smem = kProbScale * 4 + (size_t)kLinWarps * kLinStage + (size_t)kLinWarps * a.g.th * MT * sizeof(float);
-    static size_t attr = 0;
-    if (smem > attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_linear_transposed<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr = smem;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_linear_transposed<MT>, smem)) return rc;
     uint32_t items = a.g.tiles_k * a.splits, cap = (uint32_t)sm_count() * 3;
     k_linear_transposed<MT><<<items < cap ? items : cap, kLinWarps * 32, smem, s>>>(a, groups_per_split);
     CI_LAUNCH_CHECK(k_linear_transposed);
+    return CI_OK;
+}
+
+template <int MT>
+static int launch_transposed_dense(LinArgs a, uint32_t groups_per_split, cudaStream_t s) {
+    size_t smem = kProbScale * 4 + (size_t)kLinWarps * a.g.th * MT * sizeof(float);
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_linear_transposed_dense<MT>, smem)) return rc;
+    uint32_t items = a.g.tiles_k * a.splits, cap = (uint32_t)sm_count() * 3;
+    k_linear_transposed_dense<MT><<<items < cap ? items : cap, kLinWarps * 32, smem, s>>>(a, groups_per_split);
+    CI_LAUNCH_CHECK(k_linear_transposed_dense);
     return CI_OK;
 }
 
@@ -423,6 +530,21 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
 
 size_t ci_linear_allreduce_counter_bytes(void) { return 2 * sizeof(uint32_t); }
 
+int ci_linear_allreduce_qualifies(const ci_tiled_weight *w, uint32_t M) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (M == 0 || M > 2 || w->N % 2) return 0;
+    LinArgs a = base_args(w);
+    if (a.g.groups >= kTicketBytes) return 0;
+    a.M = M;
+    a.ldx = w->K;
+    a.ldy = w->N;
+    a.dry_run = 1;
+    rc = launch_linear_mma4(a, w->max_tile_len, nullptr);
+    if (rc == 1) rc = launch_linear_mma(a, w->max_tile_len, nullptr);
+    return rc == CI_OK ? 1 : (rc == 1 ? 0 : rc);
+}
+
 int ci_linear_allreduce(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M, const uint16_t *d_bias,
                         uint16_t *d_y, void *d_ws, size_t ws_bytes, void *const *peer_bufs, uint32_t capacity,
                         uint32_t *d_counter, uint32_t rank, uint32_t world, uint32_t *d_status, ci_stream_t stream) {
@@ -479,6 +601,57 @@ int ci_linear_transposed(const ci_tiled_weight *w, const uint16_t *d_x, int64_t 
         if (mc == 1) rc = launch_transposed<1>(a, gps, s);
         else if (mc == 2) rc = launch_transposed<2>(a, gps, s);
         else rc = launch_transposed<4>(a, gps, s);
+        if (rc) return rc;
+    }
+    return CI_OK;
+}
+
+int ci_linear_transposed_dense(const ci_dense_weight *w, const uint16_t *d_x, int64_t ldx, uint32_t M,
+                               const uint16_t *d_bias, uint16_t *d_y, int64_t ldy, void *d_ws, size_t ws_bytes,
+                               ci_stream_t stream) {
+    CI_REQUIRE(w != nullptr, "null weight descriptor");
+    int rc = check_tile(w->K, w->N, w->tile_h, w->tile_w);
+    if (rc) return rc;
+    CI_REQUIRE(w->states && w->stream_sizes && w->stream_offsets && w->mantissa, "null pointer in weight descriptor");
+    CI_REQUIRE(w->lut || (w->tables && w->slot_map), "neither a prepared table nor tables + slot_map given");
+    CI_REQUIRE(d_x && d_y, "null activation / output pointer");
+    if (M == 0) return CI_OK;
+    CI_REQUIRE(ldx >= (int64_t)w->N && ldy >= (int64_t)w->K, "row strides smaller than the row length");
+    LinArgs a;
+    memset(&a, 0, sizeof a);
+    a.stream = w->stream; a.states = w->states; a.tables = w->tables; a.lut = w->lut; a.slot_map = w->slot_map;
+    a.mantissa = w->mantissa; a.dense_sizes = w->stream_sizes; a.dense_offsets = w->stream_offsets;
+    a.g = make_geom(w->K, w->N, w->tile_h, w->tile_w);
+    CI_REQUIRE(a.g.tiles_k <= kTicketBytes, "too many row tiles for the ticket area");
+    CI_REQUIRE(a.g.th <= 1024, "tile height %u above 1024 is not supported by the transposed linear", a.g.th);
+    uint32_t mt_cap = a.g.th <= 256 ? 4 : (a.g.th <= 512 ? 2 : 1);
+    uint32_t target = (uint32_t)sm_count() * 6;
+    uint32_t splits = (target + a.g.tiles_k - 1) / a.g.tiles_k;
+    uint32_t by_groups = (a.g.groups + kLinWarps - 1) / kLinWarps;
+    if (splits > by_groups) splits = by_groups;
+    if (splits > kMaxSplits) splits = kMaxSplits;
+    if (splits < 1) splits = 1;
+    uint32_t gps = (a.g.groups + splits - 1) / splits;
+    a.splits = (a.g.groups + gps - 1) / gps;
+    if (a.splits > 1) {
+        CI_REQUIRE(d_ws != nullptr, "split reduction needs a workspace");
+        if (ws_bytes < workspace_bytes(M, w->K)) {
+            set_error("workspace of %zu bytes, %zu needed", ws_bytes, workspace_bytes(M, w->K));
+            return CI_E_WORKSPACE;
+        }
+    }
+    a.tickets = reinterpret_cast<uint32_t *>(d_ws);
+    a.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d_ws) + kTicketBytes * 4);
+    a.bias = d_bias; a.ldx = ldx; a.ldy = ldy;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (uint32_t m0 = 0; m0 < M; m0 += mt_cap) {
+        uint32_t mc = M - m0 < mt_cap ? M - m0 : mt_cap;
+        a.x = d_x + (size_t)m0 * ldx;
+        a.y = d_y + (size_t)m0 * ldy;
+        a.M = mc;
+        if (mc == 1) rc = launch_transposed_dense<1>(a, gps, s);
+        else if (mc == 2) rc = launch_transposed_dense<2>(a, gps, s);
+        else rc = launch_transposed_dense<4>(a, gps, s);
         if (rc) return rc;
     }
     return CI_OK;
@@ -588,9 +761,18 @@ int ci_linear_static(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx,
     if (rc) return rc;
     // The array keeps whatever the last call left.  Only the ticket counters have to start at zero (a
     // call that ended normally leaves them so; this also covers one that did not); partial sums are
-    // always written before they are read.
-    CI_CUDA(cudaMemsetAsync(scratch, 0, (size_t)ci::kTicketBytes * 4, (cudaStream_t)stream));
+    // always written before they are read.  The last word of the ticket area is the kernels' status
+    // word: it is left alone, so that a fault reported by one call can still be read after the next
+    // (ci_linear_static_status).
+    CI_CUDA(cudaMemsetAsync(scratch, 0, (size_t)(ci::kTicketBytes - 1) * 4, (cudaStream_t)stream));
     return ci_linear(w, d_x, ldx, M, d_bias, d_y, ldy, scratch, ci::kStaticScratchBytes, 0, stream);
+}
+
+int ci_linear_static_status(uint32_t *code, int clear, ci_stream_t stream) {
+    void *scratch = nullptr;
+    int rc = ci::static_scratch(&scratch);
+    if (rc) return rc;
+    return ci_status(ci_workspace_status_word(scratch), code, clear, stream);
 }
 
 }  // extern "C"

@@ -27,6 +27,7 @@ struct LinArgs {
     uint32_t *tickets;   // [items along the non-reduced dimension]
     float *partial;      // [splits][M][n_out]
     ArFuse ar;           // ar.world > 1: all-reduce the output over the ranks inside the kernel (M <= 2)
+    uint32_t dry_run;    // launchers stop before the launch: "would this weight take the staged route?"
 };
 
 struct LaneTile {

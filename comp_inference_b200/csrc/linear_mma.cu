@@ -211,6 +211,7 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
             last = seen == count - 1;
         }
         last = __shfl_sync(kFull, last, 0);
+        __syncwarp();                                           // lane 0's acquire is ordered before every lane's loads
         if (!last) return;
         if (a.M <= 2) {
             // One or two activation rows: lane = column, up to sixteen partials of both rows in flight at
@@ -460,11 +461,8 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
 
 template <uint32_t TW>
 static int launch_tw(const MmaArgs &p, uint32_t blocks, uint32_t warps, size_t smem, int max_smem, cudaStream_t s) {
-    static bool attr = false;
-    if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_linear_mma<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr = true;
-    }
+    static SmemLimit lim = {};
+    if (int rc = ensure_smem_limit(lim, (const void *)k_linear_mma<TW>, (size_t)max_smem)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks);
     cfg.blockDim = dim3(warps * 32);
@@ -524,6 +522,7 @@ int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     p.status = a.tickets + (kTicketBytes - 1);
 
     const size_t smem = fixed + (size_t)best_w * p.warp_bytes;
+    if (a.dry_run) return CI_OK;                                // qualification only
     if (g.tw == 32) return launch_tw<32>(p, blocks, best_w, smem, max_smem, s);
     if (g.tw == 16) return launch_tw<16>(p, blocks, best_w, smem, max_smem, s);
     return launch_tw<8>(p, blocks, best_w, smem, max_smem, s);

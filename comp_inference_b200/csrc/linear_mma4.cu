@@ -297,6 +297,7 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
                 if (gq < a.M && n0 < g.N) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
+                        if (n0 + 2 * j >= g.N) break;           // N need only be even: the last quad may be short
                         const float2 r = fuse_exchange_pair(a.ar, ar_seq, (gq * g.N + n0) / 2 + j, v0[2 * j], v0[2 * j + 1]);
                         v0[2 * j] = r.x;
                         v0[2 * j + 1] = r.y;
@@ -329,6 +330,7 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             last = seen == count - 1;
         }
         last = __shfl_sync(kFull, last, 0);
+        __syncwarp();                                           // lane 0's acquire is ordered before every lane's loads
         if (!last) return;
         if (a.M <= 2) {
             // One or two activation rows: lane = column, up to sixteen partials of both rows in flight at
@@ -555,13 +557,11 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     const uint32_t blocks = (warps_needed + best_w - 1) / best_w;
     p.y_vec = ((reinterpret_cast<uintptr_t>(a.y) & 15u) == 0 && (a.ldy & 7) == 0) ? 1u : 0u;
     p.status = a.tickets + (kTicketBytes - 1);
+    if (a.dry_run) return CI_OK;                                // qualification only
 
-    static bool attr = false;
-    if (!attr) {
-        CI_CUDA(cudaFuncSetAttribute(k_linear_mma4<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        CI_CUDA(cudaFuncSetAttribute(k_linear_mma4<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-        attr = true;
-    }
+    static SmemLimit lim_lo = {}, lim_hi = {};
+    if (int rc = ensure_smem_limit(lim_lo, (const void *)k_linear_mma4<false>, (size_t)max_smem)) return rc;
+    if (int rc = ensure_smem_limit(lim_hi, (const void *)k_linear_mma4<true>, (size_t)max_smem)) return rc;
     // Programmatic dependent launch: the grid may be scheduled while the previous kernel of the stream
     // drains; the kernel itself waits for that kernel before it reads activations or touches the workspace.
     cudaLaunchConfig_t cfg = {};

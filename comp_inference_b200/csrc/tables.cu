@@ -32,6 +32,17 @@ int sm_count() {
     return cached[dev];
 }
 
+int ensure_smem_limit(SmemLimit &st, const void *kernel, size_t bytes) {
+    int dev = 0;
+    CI_CUDA(cudaGetDevice(&dev));
+    CI_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+    if (st.granted[dev] < bytes) {
+        CI_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        st.granted[dev] = bytes;
+    }
+    return CI_OK;
+}
+
 int check_tile(uint32_t K, uint32_t N, uint32_t th, uint32_t tw) {
     CI_REQUIRE(K > 0 && N > 0, "empty matrix %u x %u", K, N);
     // src/cuda/rans_host.cuh:440-445: the tile height must be a multiple of 16

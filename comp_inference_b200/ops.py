@@ -3,10 +3,12 @@ kernels of libci_b200.so.  (The names still say "triton" because they are the
 public API of the reference; nothing here is Triton.)
 
     rans_decomp_triton_tiled                  comp_inference/rans_triton.py:122-168
+    rans_decomp_triton                        comp_inference/rans_triton.py:243-271 (legacy flat layout)
     fused_rans_linear_triton                  comp_inference/linear_triton.py:229-314
     fused_rans_linear_transposed_triton       comp_inference/transposed_linear_triton.py:361-435
     fused_rans_embedding_triton               comp_inference/embedding_triton.py:278-330
-    *_uncoalesced variants                    linear_triton.py:1189-1265, embedding_triton.py:431-483
+    *_uncoalesced variants                    linear_triton.py:1189-1265, embedding_triton.py:431-483,
+                                              transposed_linear_triton.py:813-883
     triton_matmul                             comp_inference/triton_gemm.py:324-337
 
 All tensor arguments must already be CUDA tensors; inputs are borrowed for the
@@ -44,6 +46,28 @@ def rans_decomp_triton_tiled(compressed_streams, initial_states, tables, slot_ma
                                 None, K, N, int(tile_k), int(tile_n), want_max=True)
     out = torch.empty((K, N), device=compressed_streams.device, dtype=torch.uint8)
     _lib.check(_lib.load().ci_decode_plane(w, _lib.ptr(out), _lib.stream()))
+    return out
+
+
+def rans_decomp_triton(compressed_streams, initial_states, tables, slot_map, stream_sizes, output_shape):
+    """Legacy flat layout: stream g = seg * width + col holds rows [512 * seg, 512 * (seg + 1)) of column col,
+    its bytes at stride len(initial_states) read from index stream_sizes[g] - 1 downwards; returns the uint8
+    plane of ``output_shape`` (comp_inference/rans_triton.py:171-271; the order RansManager.compress of the
+    reference writes, src/cuda/rans_kernels.cuh:393-509)."""
+    rows, cols = int(output_shape[0]), int(output_shape[1])
+    _lib.require_cuda(compressed_streams, "compressed stream")
+    n = int(initial_states.numel())
+    out = torch.empty((rows, cols), device=compressed_streams.device, dtype=torch.uint8)
+    if rows * cols == 0:
+        return out
+    st = _lib.as_u8(compressed_streams, "compressed stream")
+    states = _lib.as_u32(_lib.require_cuda(initial_states, "states"), "states")
+    sizes = _lib.as_u32(_lib.require_cuda(stream_sizes, "stream_sizes"), "stream_sizes")
+    tb = _lib.as_u32(_lib.require_cuda(tables, "tables"), "tables")
+    sm = _lib.as_u8(_lib.require_cuda(slot_map, "slot_map"), "slot_map")
+    _lib.check(_lib.load().ci_decode_legacy_segments(_lib.ptr(st), st.numel(), _lib.ptr(states), _lib.ptr(sizes), n,
+                                                     rows, cols, 512, _lib.ptr(tb), _lib.ptr(sm), _lib.ptr(out),
+                                                     _lib.stream()))
     return out
 
 
@@ -152,6 +176,28 @@ def fused_rans_linear_triton_uncoalesced(x, compressed_data, initial_states, tab
     _lib.check(lib.ci_linear_dense(w, _lib.ptr(x2), x2.stride(0), M, _lib.ptr(b), _lib.ptr(y), y.stride(0),
                                    _lib.ptr(ws), ws.numel(), int(SPLIT_K), _lib.stream()))
     return out if out is not None else y.view(*x.shape[:-1], N)
+
+
+def fused_rans_linear_transposed_triton_uncoalesced(x, compressed_data, initial_states, tables, slot_map,
+                                                    weight_shape, stream_offsets, stream_sizes, tile_k, tile_n,
+                                                    mantissas, workspace=None, bias=None, out=None, SPLIT_K=8):
+    """y[..., V] = x[..., H] . W[V, H]^T for a dense-layout weight stored [V, H]
+    (comp_inference/transposed_linear_triton.py:813-883).  ``workspace`` and ``SPLIT_K`` are accepted for source
+    compatibility; the split and its fp32 partials are internal."""
+    V, H = int(weight_shape[0]), int(weight_shape[1])
+    x2 = _check_x(x, H)
+    M = x2.shape[0]
+    w, keep = _lib.dense_weight(compressed_data, initial_states, stream_sizes, stream_offsets, tables, slot_map,
+                                mantissas, V, H, int(tile_k), int(tile_n))
+    lib = _lib.load()
+    y = out.view(M, V) if out is not None else torch.empty((M, V), device=x2.device, dtype=torch.bfloat16)
+    if y.dtype != torch.bfloat16 or y.stride(1) != 1:
+        raise RuntimeError("out must be a bfloat16 tensor with unit inner stride")
+    ws = _lib.workspace(x2.device, lib.ci_linear_workspace_bytes(M, V, 0, 0))
+    b = _bias(bias, V)
+    _lib.check(lib.ci_linear_transposed_dense(w, _lib.ptr(x2), x2.stride(0), M, _lib.ptr(b), _lib.ptr(y), y.stride(0),
+                                              _lib.ptr(ws), ws.numel(), _lib.stream()))
+    return out if out is not None else y.view(*x.shape[:-1], V)
 
 
 def fused_rans_embedding_triton_uncoalesced(x, compressed_data, initial_states, tables, slot_map, weight_shape,

@@ -18,20 +18,37 @@ import torch
 import torch.nn as nn
 
 from . import comp_inference as ci
-from .pytorch_runtime import patch_model
+from .pytorch_runtime import patch_model, prepare_model
 
 METADATA = {"format": "pt", "compression_method": "rans_bfloat16"}
 
 
-def compress_model(model, tile_height=1024, tile_width=32, layer_tiles=None, tied_lm_head=None):
+def _bf16_linear(m):
+    return isinstance(m, nn.Linear) and m.weight.dtype == torch.bfloat16 and m.bias is None
+
+
+def compress_model(model, tile_height=1024, tile_width=32, layer_tiles=None, tied_lm_head=None, fuse=False):
     """Compresses every bf16 nn.Linear / nn.Embedding of a Hugging Face causal LM in place, the way the
     reference's end-to-end script does (tests/test_full_model_rans.py:75-130): linears are stored
     transposed ([in, out]); the embedding table and the LM head keep their [vocab, hidden] layout.
-    ``layer_tiles`` maps a module name to (tile_height, tile_width) for per-layer tile sizes."""
+    ``layer_tiles`` maps a module name to (tile_height, tile_width) for per-layer tile sizes.
+    ``fuse``: q/k/v and gate/up projections are concatenated and compressed as one tensor each
+    (rans_compress_qkv_fused / rans_compress_gate_up_fused, as the reference's script does with its
+    fuse option, tests/test_full_model_rans.py:97-118); save such a model with ``fuse=True``."""
     layer_tiles = layer_tiles or {}
     if tied_lm_head is None:
         tied_lm_head = bool(getattr(model.config, "tie_word_embeddings", False))
+    if fuse:
+        for name, module in list(model.named_modules()):
+            if all(_bf16_linear(getattr(module, a, None)) for a in ("q_proj", "k_proj", "v_proj")):
+                th, tw = layer_tiles.get(name + ".q_proj", (tile_height, tile_width))
+                ci.rans_compress_qkv_fused(module, tile_height=th, tile_width=tw)
+            if all(_bf16_linear(getattr(module, a, None)) for a in ("gate_proj", "up_proj")):
+                th, tw = layer_tiles.get(name + ".gate_proj", (tile_height, tile_width))
+                ci.rans_compress_gate_up_fused(module, tile_height=th, tile_width=tw)
     for name, module in list(model.named_modules()):
+        if getattr(module, "compressed", None) is not None:
+            continue
         if not isinstance(module, (nn.Linear, nn.Embedding)) or module.weight.dtype != torch.bfloat16:
             continue
         is_head = name.endswith("lm_head")
@@ -72,10 +89,9 @@ def _save_rans_attributes(tensors, base, module):
         tensors[base + "bias"] = module.bias.detach().cpu()
 
 
-def pack_and_save_tensors(model, output_path: str, fuse: bool = False, tied_lm_head: bool = False):
-    """model.safetensors of a package (rans_saving.py:177-245): compressed modules under their rans_* keys,
-    every other parameter under its own name, a tied LM head dropped."""
-    from safetensors.torch import save_file
+def compressed_state_dict(model, tied_lm_head: bool = False):
+    """The tensors pack_and_save_tensors would write, as a dict (CPU tensors): what patch_model and
+    patch_model_tensor_parallel take, without the round trip through a file."""
     tensors, handled = {}, set()
     if tied_lm_head:
         handled.update({"lm_head.weight", "model.lm_head.weight"})
@@ -87,6 +103,14 @@ def pack_and_save_tensors(model, output_path: str, fuse: bool = False, tied_lm_h
     for pname, param in model.named_parameters():
         if pname not in handled:
             tensors[pname] = param.detach().cpu().contiguous()
+    return tensors
+
+
+def pack_and_save_tensors(model, output_path: str, fuse: bool = False, tied_lm_head: bool = False):
+    """model.safetensors of a package (rans_saving.py:177-245): compressed modules under their rans_* keys,
+    every other parameter under its own name, a tied LM head dropped."""
+    from safetensors.torch import save_file
+    tensors = compressed_state_dict(model, tied_lm_head=tied_lm_head)
     meta = dict(METADATA, fused_projections=str(fuse))
     save_file(tensors, output_path, metadata=meta)
     return len(tensors)
@@ -139,4 +163,4 @@ def load_compressed_model(package_dir: str, device="cuda", split_k: int = 1):
                 quant.get("default_tile_width", 32), split_k)
     if getattr(config, "tie_word_embeddings", False) and "lm_head.rans_exp_stream" not in state:
         raise RuntimeError("a package with a tied LM head needs the dense embedding to tie to; untie before compressing")
-    return model.to(device)
+    return prepare_model(model.to(device))

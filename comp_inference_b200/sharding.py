@@ -45,14 +45,12 @@ def _finish(c, stream, states, lens, man, K, N, Tk, Tn):
     return out
 
 
-def shard_rows(c, rank, world):
-    """Rows (K, the reduction dimension) [rank*K/world, (rank+1)*K/world) of a compressed [K,N] weight.
-    K/world must be a multiple of the tile height, so every shard starts on a tile row."""
+def tile_rows(c, k0, k1):
+    """Tile rows [k0, k1) of a compressed [K,N] weight as a compressed weight of its own: one contiguous
+    slice of every array.  The result covers rows [k0*th, min(k1*th, K))."""
     K, N, th, tw, Tk, Tn = _geom(c)
-    if K % world or (K // world) % th:
-        raise ValueError(f"K={K} cannot be cut into {world} row shards on {th}-row tile boundaries")
-    per = K // world // th
-    k0, k1 = rank * per, (rank + 1) * per
+    if not (0 <= k0 < k1 <= Tk):
+        raise ValueError(f"tile rows [{k0}, {k1}) outside [0, {Tk})")
     offs, lens = _i64(c["rans_exp_tile_offsets"]), c["rans_exp_tile_max_lens"]
     lens64 = _i64(lens)
     t0, t1 = k0 * Tn, k1 * Tn
@@ -61,32 +59,70 @@ def shard_rows(c, rank, world):
     stream = c["rans_exp_stream"][b0:b1]
     states = c["rans_exp_states"].reshape(Tk * Tn, 2 * tw)[t0:t1]
     man = c["rans_man_raw"].reshape(Tk * Tn, th * tw)[t0:t1]
-    return _finish(c, stream, states, lens.reshape(-1)[t0:t1], man, K // world, N, per, Tn)
+    rows = min(k1 * th, K) - k0 * th
+    return _finish(c, stream, states, lens.reshape(-1)[t0:t1], man, rows, N, k1 - k0, Tn)
 
 
-def shard_cols(c, rank, world):
-    """Columns (N, output features) [rank*N/world, (rank+1)*N/world); N/world must be a multiple of the tile width."""
+def tile_cols(c, ranges):
+    """The tile columns of the given [n0, n1) ranges (in units of tiles), concatenated in that order, as a
+    compressed weight of its own.  Every range must end on a whole tile (only the matrix's last tile column
+    may be partial, and then it must come last)."""
     K, N, th, tw, Tk, Tn = _geom(c)
-    if N % world or (N // world) % tw:
-        raise ValueError(f"N={N} cannot be cut into {world} column shards on {tw}-column tile boundaries")
-    per = N // world // tw
-    n0, n1 = rank * per, (rank + 1) * per
+    ranges = [(int(a), int(b)) for a, b in ranges]
+    for a, b in ranges:
+        if not (0 <= a < b <= Tn):
+            raise ValueError(f"tile columns [{a}, {b}) outside [0, {Tn})")
     offs = _i64(c["rans_exp_tile_offsets"]).reshape(Tk, Tn)
     lens = c["rans_exp_tile_max_lens"].reshape(Tk, Tn)
     lens64 = _i64(lens)
-    begin = offs[:, n0].tolist()
-    end = (offs[:, n1 - 1] + lens64[:, n1 - 1] * 2 * tw).tolist()
     src = c["rans_exp_stream"]
-    pieces = [src[int(b):int(e)] for b, e in zip(begin, end)]       # one contiguous run per tile row
+    begins = [offs[:, a].tolist() for a, _ in ranges]
+    ends = [(offs[:, b - 1] + lens64[:, b - 1] * 2 * tw).tolist() for _, b in ranges]
+    pieces = [src[int(begins[j][k]):int(ends[j][k])] for k in range(Tk) for j in range(len(ranges))]
     stream = torch.cat(pieces) if pieces else src[:0]
-    states = c["rans_exp_states"].reshape(Tk, Tn, 2 * tw)[:, n0:n1]
-    man = c["rans_man_raw"].reshape(Tk, Tn, th * tw)[:, n0:n1]
-    return _finish(c, stream, states, lens[:, n0:n1], man, K, N // world, Tk, per)
+    st = c["rans_exp_states"].reshape(Tk, Tn, 2 * tw)
+    mn = c["rans_man_raw"].reshape(Tk, Tn, th * tw)
+    states = torch.cat([st[:, a:b] for a, b in ranges], dim=1)
+    man = torch.cat([mn[:, a:b] for a, b in ranges], dim=1)
+    new_lens = torch.cat([lens[:, a:b] for a, b in ranges], dim=1)
+    cols = sum(min(b * tw, N) - a * tw for a, b in ranges)
+    return _finish(c, stream, states, new_lens, man, K, cols, Tk, sum(b - a for a, b in ranges))
+
+
+def shard_rows(c, rank, world):
+    """Rows (K, the reduction dimension) [rank*K/world, (rank+1)*K/world) of a compressed [K,N] weight.
+    K/world must be a multiple of the tile height, so every shard starts on a tile row."""
+    K, N, th, tw, Tk, Tn = _geom(c)
+    if K % world or (K // world) % th:
+        raise ValueError(f"K={K} cannot be cut into {world} row shards on {th}-row tile boundaries")
+    per = K // world // th
+    return tile_rows(c, rank * per, (rank + 1) * per)
+
+
+def shard_cols(c, rank, world, parts=None):
+    """Columns (N, output features) [rank*N/world, (rank+1)*N/world); N/world must be a multiple of the tile
+    width.  ``parts``: widths of the blocks a concatenated projection consists of (q|k|v, gate|up); the shard
+    is then the rank's slice of every block, concatenated in the same order, so that each rank holds whole
+    heads of q, k and v (or matching gate and up columns)."""
+    K, N, th, tw, Tk, Tn = _geom(c)
+    parts = [N] if parts is None else [int(p) for p in parts]
+    if sum(parts) != N:
+        raise ValueError(f"parts {parts} do not add up to N={N}")
+    ranges, start = [], 0
+    for p in parts:
+        if p % world or (p // world) % tw or start % tw:
+            raise ValueError(f"a block of {p} columns cannot be cut into {world} column shards on {tw}-column tile boundaries")
+        per = p // world // tw
+        ranges.append((start // tw + rank * per, start // tw + (rank + 1) * per))
+        start += p
+    return tile_cols(c, ranges)
 
 
 def can_shard_rows(K, th, world):
     return K % world == 0 and (K // world) % th == 0
 
 
-def can_shard_cols(N, tw, world):
-    return N % world == 0 and (N // world) % tw == 0
+def can_shard_cols(N, tw, world, parts=None):
+    parts = [N] if parts is None else parts
+    return all(p % world == 0 and (p // world) % tw == 0 for p in parts) and all(
+        sum(parts[:i]) % tw == 0 for i in range(len(parts)))

@@ -86,6 +86,35 @@ typedef struct ci_dense_weight {
 int ci_abi_version(void);
 const char *ci_last_error(void);
 
+/* ---- errors found on the device, malformed metadata ---------------------- */
+
+/* The staged kernels never trap and never wait without a bound.  When a wait runs out, or a tile's
+ * entry in tile_max_lens contradicts the descriptor's max_tile_len, they write a code into a status
+ * word and finish with invalid output: 1 = a copy into shared memory did not arrive, 2 = metadata
+ * mismatch, 9 = a peer rank did not answer (the tensor-parallel exchanges), other values = a pipeline
+ * stage of the prefill GEMM gave up.  For ci_linear / ci_linear_transposed / ci_linear_dense the word
+ * lives inside the workspace, at the address ci_workspace_status_word() returns (host arithmetic, no
+ * CUDA call); the exchanges take a d_status argument of their own.
+ *
+ * ci_status copies a status word to the host on `stream` and WAITS for the stream.  0: the word was
+ * zero.  CI_E_DEVICE: it was not; *code (may be NULL) receives it, ci_last_error() says what it means,
+ * and with clear != 0 the word is reset so that later calls start clean.  This is the path the
+ * reference lacks: its encoder's overflow flag is a by-value kernel argument that never reaches the
+ * host (src/cuda/rans_kernels.cuh:145, src/cuda/rans_host.cuh:505-541). */
+uint32_t *ci_workspace_status_word(void *d_workspace);
+int ci_status(uint32_t *d_status_word, uint32_t *code, int clear, ci_stream_t stream);
+
+/* Host.  Consistency of a tiled weight's metadata, given as HOST copies, before any kernel touches
+ * it: tile count against the shape, every tile's byte block [offset, offset + max_len * 2 * tile_w)
+ * inside the stream and not overlapping its predecessor, max_len <= tile_h (a symbol emits at most two
+ * bytes) and <= max_tile_len when that is non-zero, n_states = tiles * 2 * tile_w, mantissa_len (0 =
+ * not given) >= tiles * tile_h * tile_w, and -- when tables / slot_map are given -- frequencies that
+ * sum to 4096 with matching cumulative values and slot map.  CI_E_INVALID names the first offender.
+ * The reference loads whatever the file holds (comp_inference/pytorch_runtime.py:631-637). */
+int ci_validate_tiled_metadata(const uint32_t *tile_offsets, const uint32_t *tile_max_lens, const uint32_t *tables,
+                               const uint8_t *slot_map, uint64_t stream_len, uint64_t n_states, uint64_t mantissa_len,
+                               uint32_t K, uint32_t N, uint32_t tile_h, uint32_t tile_w, uint32_t max_tile_len);
+
 /* Device properties the host side sizes launches with (SM count etc.); fills
  * sm_count / max dynamic shared memory per block of the current device. */
 int ci_device_info(int *sm_count, int *max_smem_per_block);
@@ -207,6 +236,10 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_strid
 size_t ci_linear_static_max_bytes(void);
 int ci_linear_static(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M,
                      const uint16_t *d_bias, uint16_t *d_y, int64_t y_row_stride, ci_stream_t stream);
+/* ci_status for the built-in array of ci_linear_static (the caller has no pointer to it).  The status
+ * word is not touched by the per-call clearing of the ticket counters, so a code written by one call
+ * is still there after the next.  Allocates nothing; waits for `stream`.  No counterpart in the reference. */
+int ci_linear_static_status(uint32_t *code, int clear, ci_stream_t stream);
 
 /* y[M,V] = x[M,H] . W[V,H]^T for a weight stored as [K=V, N=H] (LM head / tied
  * embedding).  Replaces fused_rans_linear_transposed_triton
@@ -227,6 +260,12 @@ int ci_linear_dense(const ci_dense_weight *w, const uint16_t *d_x, int64_t x_row
                     size_t workspace_bytes, uint32_t split_k, ci_stream_t stream);
 int ci_embedding_dense(const ci_dense_weight *w, const int64_t *d_ids, uint64_t n_ids, uint16_t *d_out,
                        int64_t out_row_stride, ci_stream_t stream);
+/* Dense-layout LM head: y[M,V] = x[M,H] . W[V,H]^T for W stored [K=V, N=H], one stream per tile column.
+ * Replaces fused_rans_linear_transposed_triton_uncoalesced
+ * (comp_inference/transposed_linear_triton.py:660-883). */
+int ci_linear_transposed_dense(const ci_dense_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M,
+                               const uint16_t *d_bias, uint16_t *d_y, int64_t y_row_stride, void *d_workspace,
+                               size_t workspace_bytes, ci_stream_t stream);
 
 /* ---- legacy flat layout -------------------------------------------------- */
 
@@ -250,6 +289,22 @@ int ci_encode_legacy_sizes(const uint8_t *d_data, uint64_t n, uint32_t num_strea
 int ci_encode_legacy_write(const uint8_t *d_data, uint64_t n, uint32_t num_streams, const uint16_t *freqs,
                            const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len, ci_stream_t stream);
 
+/* The same flat byte arrangement with the symbol-to-stream assignment of the reference's legacy ENCODER
+ * (src/cuda/rans_kernels.cuh:393-509) and of its Triton decoder rans_decomp_triton
+ * (comp_inference/rans_triton.py:171-271): the plane is a row-major [rows, cols] matrix, stream
+ * g = seg * cols + col codes rows [seg * seg_rows, + seg_rows) of column col (the reference fixes
+ * seg_rows = 512); num_streams = ceil(rows / seg_rows) * cols. */
+int ci_decode_legacy_segments(const uint8_t *d_stream, uint64_t stream_len, const uint32_t *d_states,
+                              const uint32_t *d_sizes, uint32_t num_streams, uint32_t rows, uint32_t cols,
+                              uint32_t seg_rows, const uint32_t *d_tables, const uint8_t *d_slot_map, uint8_t *d_out,
+                              ci_stream_t stream);
+int ci_encode_legacy_segments_sizes(const uint8_t *d_data, uint32_t rows, uint32_t cols, uint32_t seg_rows,
+                                    const uint16_t *freqs, const uint16_t *cdf, uint32_t *d_states, uint32_t *d_sizes,
+                                    ci_stream_t stream);
+int ci_encode_legacy_segments_write(const uint8_t *d_data, uint32_t rows, uint32_t cols, uint32_t seg_rows,
+                                    const uint16_t *freqs, const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len,
+                                    ci_stream_t stream);
+
 /* ---- tensor-parallel exchange ---------------------------------------------- */
 
 /* One-shot all-reduce (sum) of a small bf16 tensor over peer memory, for the outputs of row-parallel linears.
@@ -264,6 +319,17 @@ size_t ci_allreduce_buffer_bytes(uint32_t world, uint32_t capacity);
 size_t ci_allreduce_counter_bytes(void);
 int ci_allreduce_oneshot(const uint16_t *d_in, uint16_t *d_out, uint32_t n, uint32_t capacity, void *const *peer_bufs,
                          uint32_t *d_counters, uint32_t rank, uint32_t world, uint32_t *d_status, ci_stream_t stream);
+/* One-shot all-gather with the same buffers, protocol and bounds: every rank contributes a bf16 block
+ * [rows, cols] (cols even, rows * cols <= capacity) and receives d_out[rows, world * cols] with rank q's block in
+ * columns [q * cols, (q + 1) * cols) -- the logits of a vocabulary-parallel LM head.  Give it a buffer and
+ * counters of its own (do not share them with an all-reduce: the call sequences are counted per buffer).
+ * d_in and d_out must differ.  No counterpart in the reference; a port would call an NCCL all-gather. */
+int ci_allgather_oneshot(const uint16_t *d_in, uint16_t *d_out, uint32_t rows, uint32_t cols, uint32_t capacity,
+                         void *const *peer_bufs, uint32_t *d_counters, uint32_t rank, uint32_t world, uint32_t *d_status,
+                         ci_stream_t stream);
+/* How often ci_allreduce_oneshot re-reads a slot before it gives up on a peer (process-wide; 0 restores
+ * the default of about a second).  For tests of the give-up path and for hosts with their own watchdog. */
+void ci_allreduce_set_poll_limit(uint32_t polls);
 
 /* Row-parallel fused decode-linear with the all-reduce inside the kernel: y[M, N] = sum over ranks of
  * x_rank[M, K_rank] . W_rank[K_rank, N] (+ bias, added once after the sum).  The warps that hold a column group's
@@ -273,6 +339,11 @@ int ci_allreduce_oneshot(const uint16_t *d_in, uint16_t *d_out, uint32_t n, uint
  * of zeroed local memory.  Returns CI_E_INVALID when the weight does not qualify for the staged GEMV kernels
  * (the caller then runs ci_linear followed by ci_allreduce_oneshot).  No counterpart in the reference. */
 size_t ci_linear_allreduce_counter_bytes(void);
+/* 1 if ci_linear_allreduce would take this weight for M rows, 0 if it would answer CI_E_INVALID, < 0 on a
+ * malformed descriptor.  Launches nothing.  Shards differ in their deepest tile, so the answer can differ
+ * between ranks: a tensor-parallel group takes the minimum over its ranks once, at set-up, and all ranks
+ * then use the same route for that layer. */
+int ci_linear_allreduce_qualifies(const ci_tiled_weight *w, uint32_t M);
 int ci_linear_allreduce(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_stride, uint32_t M,
                         const uint16_t *d_bias, uint16_t *d_y, void *d_workspace, size_t workspace_bytes,
                         void *const *peer_bufs, uint32_t capacity, uint32_t *d_counter, uint32_t rank, uint32_t world,
