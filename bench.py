@@ -2,21 +2,29 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch M]
 
-Workload (named in the JSON line's ``config.workload``): the fused decode-GEMV of the seven linear
-layers of one Llama-2-7B decoder block (q, k, v, o: 4096x4096; gate, up: 4096->11008; down:
-11008->4096), weights seeded N(0, 0.02) bf16, rANS-compressed in the reference's tiled stream layout
-(tile 128x32), activation batch M (default 1).  One "step" is one token batch through the seven
-layers; about 290 MB of compressed weights are read per step, more than twice the L2, so every step
-streams from HBM.  ``value`` is tokens/s with all inputs resident in HBM (one CUDA graph replay per
-step, timed with CUDA events); ``e2e`` is the same work through the public module API
-(RansLinear.forward) the way a serving loop runs a decode step: host-to-device copy of the activations
-from pinned memory, the seven module calls and the copy of the result back to pinned host memory are
-captured once with torch.cuda.graph and replayed, the host waiting for the result after every step.
+Workload (named in the JSON line's ``config.workload``): the fused decode-GEMV of the linear layers of one
+Llama-2-7B decoder block (q, k, v, o: 4096x4096; gate, up: 4096->11008; down: 11008->4096), weights seeded
+N(0, 0.02) bf16, rANS-compressed in the reference's tiled stream layout (tile 128x32), activation batch M
+(default 1).  q|k|v and gate|up are stored and run as one concatenated matrix each, which is what the
+reference's rans_compress_qkv_fused / rans_compress_gate_up_fused produce, so a step is four launches over
+the same seven weights.  One "step" is one token batch through the block; about 290 MB of compressed weights
+are read per step, more than twice the L2, so every step streams from HBM.  ``value`` is tokens/s with all
+inputs resident in HBM (one CUDA graph replay per step, timed with CUDA events; the ``steps`` replays are
+repeated several times and the median is reported with the spread); ``e2e`` is the same work through the
+public module API the way a serving loop runs a decode step: host-to-device copy of the activations from
+pinned memory, the module calls and the copy of the result back to pinned host memory are captured once with
+torch.cuda.graph and replayed, the host waiting for the result after every step.
 
-With --gpus N > 1 (launched under torch.distributed.run) the block is tensor parallel: q/k/v/gate/up
+With --gpus N > 1 (launched under torch.distributed.run) the block is tensor parallel: qkv and gate|up
 are column shards, o/down row shards cut out of the compressed arrays, with an all-reduce of the
-activations after o and down (a one-shot kernel over peer memory, NCCL where that is unavailable);
-every rank decodes only its own shard.  Total work is fixed as N grows ("strong" scaling).
+activations after o and down (inside the GEMV kernel over peer memory; a one-shot kernel or NCCL where that
+is unavailable); every rank decodes only its own shard.  Total work is fixed as N grows ("strong" scaling).
+Rank 0 also runs the unsharded block and the line carries the relative error of the N-rank result.
+
+``extra.full_model`` (every N): the whole Llama-2-7B architecture (32 layers, random init from a seed), every
+linear, the embedding table and the LM head compressed through the public API and loaded with patch_model /
+patch_model_tensor_parallel; a 512-token prompt and 128 greedy tokens at batch 1 and 8, wall-clock tokens/s,
+with the first-step logits and the greedy tokens compared against the dense bf16 model.
 
 --impl reference times the CPU restatement of the reference's algorithm (the oracle; the reference
 ships no CPU codec) on the host cores, on the same workload, metric and unit.
@@ -24,6 +32,7 @@ ships no CPU codec) on the host cores, on the same workload, metric and unit.
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -32,23 +41,29 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer buffers are never bound to a multicast object
 
 import numpy as np
 import torch
 
 TILE_H, TILE_W = 128, 32
-HIDDEN, FFN = 4096, 11008
-# name, in_features (K), out_features (N), seed, tensor-parallel kind
-LAYERS = [("q_proj", HIDDEN, HIDDEN, 1001, "col"), ("k_proj", HIDDEN, HIDDEN, 1011, "col"),
-          ("v_proj", HIDDEN, HIDDEN, 1021, "col"), ("o_proj", HIDDEN, HIDDEN, 1031, "row"),
-          ("gate_proj", HIDDEN, FFN, 1002, "col"), ("up_proj", HIDDEN, FFN, 1012, "col"),
-          ("down_proj", FFN, HIDDEN, 1003, "row")]
+HIDDEN, FFN, VOCAB = 4096, 11008, 32000
+# HF name, in_features (K), out_features (N), seed -- the seven weights of the block
+WEIGHTS = {"q_proj": (HIDDEN, HIDDEN, 1001), "k_proj": (HIDDEN, HIDDEN, 1011), "v_proj": (HIDDEN, HIDDEN, 1021),
+           "o_proj": (HIDDEN, HIDDEN, 1031), "gate_proj": (HIDDEN, FFN, 1002), "up_proj": (HIDDEN, FFN, 1012),
+           "down_proj": (FFN, HIDDEN, 1003)}
+# launch name, the weights concatenated along the output dimension, tensor-parallel kind
+LAYERS = [("qkv_proj", ("q_proj", "k_proj", "v_proj"), "col"), ("o_proj", ("o_proj",), "row"),
+          ("gate_up_proj", ("gate_proj", "up_proj"), "col"), ("down_proj", ("down_proj",), "row")]
 METRIC = "fused decode-GEMV tok/s (one Llama-2-7B decoder block: 7 rANS-compressed linears)"
-# DRAM bytes (read + write) per launch of the fused kernel from one ncu capture of the 4096x4096 layer
-# (profiles/linear_mma4_4096x4096_tile128.md); traffic grows with the compressed size, so a step's
-# average launch is scaled by its compressed bytes.
+REPEATS = 7
+# DRAM bytes (read + write) per launch of the fused kernel from the most recent ncu capture of the 4096x4096
+# layer at tile 128x32 (24.06 MB of compressed bytes + activations); traffic grows in proportion to the
+# compressed size, so a step's average launch is scaled by its compressed bytes.
 NCU_TRAFFIC_4096 = 24.17e6
 NCU_BYTES_4096 = 24.06e6
+NCU_CAPTURE = "ncu --set full of k_linear_mma4 on the 4096x4096 layer (bench.py --kernels-once), scaled by compressed bytes"
+ROUTES = {0: "k_linear (generic split-K)", 1: "k_linear_mma", 2: "k_linear_mma4", 3: "k_linear_gemm"}
 
 
 def trace(msg):
@@ -67,11 +82,17 @@ def make_weight_kn(K, N, seed):
     return (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).t().contiguous()
 
 
+def make_fused_kn(names):
+    """The named weights of the block side by side: [K, sum of N]."""
+    return torch.cat([make_weight_kn(*WEIGHTS[n]) for n in names], dim=1).contiguous()
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
-        return float(json.load(open(path))["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", 1377.6)), "measured"
+    return 6650.0, 1400.0, "fallback"
 
 
 class ClockSampler(threading.Thread):
@@ -104,19 +125,57 @@ class ClockSampler(threading.Thread):
                 "reasons": reasons, "samples": len(mhz)}
 
 
+def timed(fn, iters, warm=3):
+    """Mean milliseconds per call of fn over `iters` back-to-back calls (CUDA events, current stream)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def graphed(fn):
+    """fn captured in a CUDA graph on a side stream (after one eager run there); returns the graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        fn()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+    torch.cuda.synchronize()
+    return graph
+
+
 # ------------------------------------------------------------------------------------------- ours
 
-def build_block(rank, world, device):
+def compressed_bytes(c):
+    return sum(c[key].numel() * c[key].element_size() for key in
+               ("rans_exp_stream", "rans_exp_states", "rans_exp_tile_offsets", "rans_exp_tile_max_lens",
+                "rans_man_raw")) + 1024 + 4096
+
+
+def build_block(rank, world, device, keep_dense=False):
     """Compressed modules of this rank's part of the block, plus byte counts for the roofline."""
     import comp_inference_b200 as ci
     from comp_inference_b200 import sharding
-    mods, wbytes, notes = {}, 0, []
-    for name, K, N, seed, kind in LAYERS:
-        Wkn = make_weight_kn(K, N, seed).to(device)
+    mods, wbytes, notes, dense = {}, 0, [], {}
+    for name, members, kind in LAYERS:
+        parts = [WEIGHTS[m][1] for m in members]
+        K = WEIGHTS[members[0]][0]
+        Wkn = make_fused_kn(members).to(device)
+        if keep_dense:
+            dense[name] = Wkn
         if world == 1:
             c = ci.compress_weight_cuda(Wkn, TILE_H, TILE_W)
         elif kind == "col":
-            c = sharding.shard_cols(ci.compress_weight_cuda(Wkn, TILE_H, TILE_W), rank, world)
+            c = sharding.shard_cols(ci.compress_weight_cuda(Wkn, TILE_H, TILE_W), rank, world, parts)
         elif sharding.can_shard_rows(K, TILE_H, world):
             c = sharding.shard_rows(ci.compress_weight_cuda(Wkn, TILE_H, TILE_W), rank, world)
         else:
@@ -131,45 +190,58 @@ def build_block(rank, world, device):
             m = ci.RansRowParallelLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
         else:
             m = ci.RansLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
+        m.first_part = parts[0] // world                        # width of the block that feeds the next layer
         mods[name] = m
-        wbytes += sum(c[key].numel() * c[key].element_size() for key in
-                      ("rans_exp_stream", "rans_exp_states", "rans_exp_tile_offsets", "rans_exp_tile_max_lens",
-                       "rans_man_raw")) + 1024 + 4096
-    return mods, wbytes, notes
+        wbytes += compressed_bytes(c)
+    return mods, wbytes, notes, dense
 
 
-def block_step(mods, x, world):
-    """One token batch through the seven linears (attention and the SwiGLU product are outside the hot
-    path and left out; the data flow between the layers is real).  With N > 1, o_proj and down_proj are
-    RansRowParallelLinear: they all-reduce their output themselves (inside the GEMV kernel for one or two
-    rows, else with the one-shot kernel or NCCL)."""
-    q = mods["q_proj"](x)
-    mods["k_proj"](x)
-    mods["v_proj"](x)
-    h = mods["o_proj"](q)                       # column shard of q feeds the row shard of o
-    g = mods["gate_proj"](h)
-    mods["up_proj"](h)
-    return mods["down_proj"](g)
+def block_step(mods, x):
+    """One token batch through the block's linears (attention and the SwiGLU product are outside the hot
+    path and left out; the data flow between the layers is real: the q block of qkv feeds o, the gate block of
+    gate|up feeds down).  With N > 1, o_proj and down_proj are RansRowParallelLinear: they all-reduce their
+    output themselves (inside the GEMV kernel for one or two rows, else with the one-shot kernel or NCCL)."""
+    qkv = mods["qkv_proj"](x)
+    h = mods["o_proj"](qkv[..., :mods["qkv_proj"].first_part])
+    gu = mods["gate_up_proj"](h)
+    return mods["down_proj"](gu[..., :mods["gate_up_proj"].first_part])
 
 
-def secondary_metrics(mods, device):
-    """The other two halves of the headline metric on the same block, N = 1 only, short runs outside the
-    timed region: stand-alone rANS decode (effective uncompressed GB/s) and prefill through the tcgen05
-    decode-GEMM (tokens/s at 512 activation rows)."""
+def block_routes(mods, M):
+    from comp_inference_b200 import _lib
+    lib = _lib.load()
+    return sorted({ROUTES.get(lib.ci_linear_route(m._weight(m.in_features, m.out_features), M), "?")
+                   for m in mods.values()})
+
+
+def parity_table(mods, dense, device):
+    """Per-shape error of the fused linear against fp32 matmul on the dense weight: the figures the parity
+    tests assert, reported instead of thrown away.  max_rel = max|y - ref| / max|ref|; allclose = the
+    reference's own criterion |y - ref| <= 1e-2 + 1e-2 |ref| (tests/test_mat_mul.py:220), as the fraction of
+    elements that meet it."""
+    rows = []
+    for name, m in mods.items():
+        W = dense[name].float()
+        for M in (1, 4, 16, 512):
+            x = torch.randn(M, m.in_features, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).to(device)
+            y = m(x).float()
+            ref = x.float() @ W
+            err = (y - ref).abs()
+            rows.append({"layer": name, "K": m.in_features, "N": m.out_features, "M": M,
+                         "max_rel": float(err.max() / ref.abs().max()),
+                         "allclose_1e-2": float((err <= 1e-2 + 1e-2 * ref.abs()).float().mean())})
+        del W
+    return rows
+
+
+def secondary_metrics(mods, dense, device, peak_hbm, peak_tf, src):
+    """The other parts of the headline metric on the same block, N = 1 only, short runs outside the timed
+    region."""
     import comp_inference_b200 as ci
+    from comp_inference_b200 import ops
+    out = {}
 
-    def timed(fn, iters):
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / iters
-
+    # ---- stand-alone rANS decode to bf16
     def decode_all():
         for m in mods.values():
             ci.rans_decompress_bf16(m.rans_exp_stream, m.rans_exp_states, m.rans_exp_tables, m.rans_exp_slot_map,
@@ -178,41 +250,225 @@ def secondary_metrics(mods, device):
 
     dense_bytes = sum(2 * m.in_features * m.out_features for m in mods.values())
     ms = timed(decode_all, 10)
-    peak, src = peaks()
-    out = {"decode_bf16": {"effective_uncompressed_GBs": dense_bytes / (ms * 1e-3) / 1e9, "ms_per_block": ms,
-                           "frac_of_hbm_peak": dense_bytes / (ms * 1e-3) / 1e9 / peak, "peak_source": f"of {src}"}}
-    x = torch.randn(512, HIDDEN, generator=torch.Generator().manual_seed(2512)).to(torch.bfloat16).to(device)
-    ms = timed(lambda: block_step(mods, x, 1), 10)
-    flops = sum(2.0 * 512 * m.in_features * m.out_features for m in mods.values())
-    out["prefill_M512"] = {"tok_s": 512 / (ms * 1e-3), "ms_per_block": ms, "TFLOPs": flops / (ms * 1e-3) / 1e12,
-                           "kernel": "k_linear_gemm (tcgen05.mma, TMEM accumulators)"}
-    # the same 512 rows through the reference's other prefill route: stand-alone decode into a scratch buffer,
-    # then a library GEMM (RansLinear(prefill_policy="decode_then_gemm"))
-    for m in mods.values():
-        m.prefill_policy = "decode_then_gemm"
-    ms = timed(lambda: block_step(mods, x, 1), 10)
-    for m in mods.values():
-        m.prefill_policy = "fused"
-    out["prefill_M512_decode_then_gemm"] = {"tok_s": 512 / (ms * 1e-3), "ms_per_block": ms,
-                                            "TFLOPs": flops / (ms * 1e-3) / 1e12,
-                                            "kernel": "k_decode4 into an L2-sized scratch + cuBLAS bf16 GEMM"}
-    # vocabulary table 32000 x 4096 stored [V, H]: row gather of 4096 ids, and the LM head at batch 1
-    V = 32000
-    table = make_weight_kn(V, HIDDEN, 1004).to(device)
-    c = ci.compress_weight_cuda(table, TILE_H, TILE_W)
-    emb = ci.RansEmbedding(V, HIDDEN, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
-    head = ci.RansLMHead(HIDDEN, V, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
-    ids = torch.randint(0, V, (4096,), generator=torch.Generator().manual_seed(3001)).to(device)
-    rows = emb(ids)
-    exact = bool(torch.equal(rows.view(torch.int16), table[ids].view(torch.int16)))
-    ms = timed(lambda: emb(ids), 10)
-    out["embedding_4096_ids"] = {"ms": ms, "out_GBs": 4096 * HIDDEN * 2 / (ms * 1e-3) / 1e9, "bit_exact": exact,
-                                 "symbols_decoded_per_emitted": (TILE_H // 2 + 1) / 2.0}
+    out["decode_bf16"] = {"effective_uncompressed_GBs": dense_bytes / (ms * 1e-3) / 1e9, "ms_per_block": ms,
+                          "frac_of_hbm_peak": dense_bytes / (ms * 1e-3) / 1e9 / peak_hbm, "peak_source": f"of {src}"}
+
+    # ---- GPU encoder: whole pipeline (split, histogram, table, two encoder passes) and the encoder calls alone
+    W = dense["gate_up_proj"]
+    ms = timed(lambda: ci.compress_weight_cuda(W, TILE_H, TILE_W), 3, warm=1)
+    e, _ = ci.extract_exp_and_mantissa(W)
+    f, cdf = ci.get_rans_lut(e)
+    mgr = ci.ccore.RansManager(e.numel())
+    ms_enc = timed(lambda: mgr.compress_tiled(e, f, cdf, TILE_H, TILE_W, _keep_on_device=True), 3, warm=1)
+    out["encode"] = {"shape_KN": list(W.shape), "pipeline_ms": ms, "pipeline_bf16_in_GBs": W.numel() * 2 / (ms * 1e-3) / 1e9,
+                     "encoder_ms": ms_enc, "encoder_symbols_per_s": W.numel() / (ms_enc * 1e-3),
+                     "note": "encoder_ms = both passes (sizes, write) + the host wait between them"}
+    del e
+
+    # ---- small batches through the block, ours and the dense library GEMV on the same rotation (> L2)
+    dense7 = {}
+    for name, members, _ in LAYERS:                             # the seven weights on their own, as the reference holds them
+        start = 0
+        for n in members:
+            dense7[n] = dense[name][:, start:start + WEIGHTS[n][1]].contiguous()
+            start += WEIGHTS[n][1]
+
+    def dense_block7(x):
+        q = torch.matmul(x, dense7["q_proj"])
+        torch.matmul(x, dense7["k_proj"])
+        torch.matmul(x, dense7["v_proj"])
+        h = torch.matmul(q, dense7["o_proj"])
+        g = torch.matmul(h, dense7["gate_proj"])
+        torch.matmul(h, dense7["up_proj"])
+        return torch.matmul(g, dense7["down_proj"])
+
+    def dense_block4(x):
+        qkv = torch.matmul(x, dense["qkv_proj"])
+        h = torch.matmul(qkv[..., :HIDDEN], dense["o_proj"])
+        gu = torch.matmul(h, dense["gate_up_proj"])
+        return torch.matmul(gu[..., :FFN], dense["down_proj"])
+
+    small = {}
+    for M in (1, 4, 16):
+        x = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).to(device)
+        g_ours = graphed(lambda: block_step(mods, x))
+        g7 = graphed(lambda: dense_block7(x))
+        g4 = graphed(lambda: dense_block4(x))
+        t_ours, t7, t4 = (timed(g.replay, 50, warm=5) for g in (g_ours, g7, g4))
+        small[f"batch{M}"] = {"ours_ms": t_ours, "cublas_7_matmuls_ms": t7, "cublas_4_fused_matmuls_ms": t4,
+                              "ours_over_cublas7": t7 / t_ours, "ours_tok_s": M / (t_ours * 1e-3),
+                              "kernels": block_routes(mods, M)}
+        del g_ours, g7, g4
+    out["block_small_batches"] = dict(small, note="one CUDA graph replay per step each; cuBLAS = torch.matmul on the "
+                                      "dense bf16 weights [K,N] (the reference's baseline call, tests/test_split_k.py:153), "
+                                      "405 MB per step, the same > L2 rotation")
+    del dense7
+
+    # ---- prefill: 512 and 2048 rows, split-K 1/2/4/8 and the library's own choice, and decode + cuBLAS
+    flops_per_row = sum(2.0 * m.in_features * m.out_features for m in mods.values())
+
+    def block_split(x, split_k):
+        def lin(m, xx):
+            x2 = ops._check_x(xx, m.in_features)
+            return ops._linear_call(m._weight(m.in_features, m.out_features), x2, x2.shape[0], m.out_features, None,
+                                    None, split_k, False)
+        qkv = lin(mods["qkv_proj"], x)
+        h = lin(mods["o_proj"], qkv[..., :HIDDEN])
+        gu = lin(mods["gate_up_proj"], h)
+        return lin(mods["down_proj"], gu[..., :FFN])
+
+    from comp_inference_b200 import _lib
+    _lib.reserve_workspace(device, (1 << 16) + 8 * 2048 * 2 * FFN * 4)   # room for 8 partial sums of the widest layer
+    prefill = {}
+    for M in (512, 2048):
+        x = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).to(device)
+        row = {}
+        for sk in (0, 1, 2, 4, 8):
+            ms = timed(lambda: block_split(x, sk), 5)
+            row["auto" if sk == 0 else f"split_k{sk}"] = {
+                "ms_per_block": ms, "tok_s": M / (ms * 1e-3), "TFLOPs": flops_per_row * M / (ms * 1e-3) / 1e12,
+                "frac_of_bf16_peak": flops_per_row * M / (ms * 1e-3) / 1e12 / peak_tf}
+        for m in mods.values():
+            m.prefill_policy = "decode_then_gemm"
+        ms = timed(lambda: block_step(mods, x), 5)
+        for m in mods.values():
+            m.prefill_policy = "fused"
+        row["decode_then_gemm"] = {"ms_per_block": ms, "tok_s": M / (ms * 1e-3),
+                                   "TFLOPs": flops_per_row * M / (ms * 1e-3) / 1e12,
+                                   "kernel": "k_decode4 into a scratch buffer + cuBLAS bf16 GEMM"}
+        prefill[f"M{M}"] = row
+    out["prefill"] = dict(prefill, kernel="k_linear_gemm (tcgen05.mma, TMEM accumulators)", peak_source=f"of {src} sustained bf16")
+    out["prefill_M512"] = dict(prefill["M512"]["auto"], kernel="k_linear_gemm (tcgen05.mma, TMEM accumulators)")
+    out["prefill_M512_decode_then_gemm"] = prefill["M512"]["decode_then_gemm"]
+
+    # ---- vocabulary table 32000 x 4096 stored [V, H]: row gather of 4096 ids by tile height; LM head at batch 1
+    table = make_weight_kn(VOCAB, HIDDEN, 1004).to(device)           # generated as [H, V] -> stored [V, H]
+    ids = torch.randint(0, VOCAB, (4096,), generator=torch.Generator().manual_seed(3001)).to(device)
+    sweep, best = {}, None
+    for th in (16, 32, 64, 128):
+        c = ci.compress_weight_cuda(table, th, TILE_W)
+        emb = ci.RansEmbedding(VOCAB, HIDDEN, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
+        rows = emb(ids)
+        exact = bool(torch.equal(rows.view(torch.int16), table[ids].view(torch.int16)))
+        ms = timed(lambda: emb(ids), 10)
+        half = th // 2
+        sweep[f"tile_h{th}"] = {"ms": ms, "out_GBs": 4096 * HIDDEN * 2 / (ms * 1e-3) / 1e9, "bit_exact": exact,
+                                "bytes_per_weight": compressed_bytes(c) / (VOCAB * HIDDEN),
+                                "symbols_decoded_per_emitted": float(((ids % half) + 1).float().mean())}
+        if best is None or ms < sweep[best]["ms"]:
+            best = f"tile_h{th}"
+        if th == TILE_H:
+            head_c = c
+        del emb
+    out["embedding_tile_sweep"] = sweep
+    out["embedding_4096_ids"] = dict(sweep[best], tile=best,
+                                     note="the format stores the tile size per tensor; the table takes the height that "
+                                          "minimises the gather (a stream cannot be entered in the middle)")
+    head = ci.RansLMHead(HIDDEN, VOCAB, head_c["tile_height"], head_c["tile_width"]).load_compressed(head_c).to(device)
+    head.prepare()
     x1 = torch.randn(1, HIDDEN, generator=torch.Generator().manual_seed(2001)).to(torch.bfloat16).to(device)
-    head(x1)                                                       # builds the transposed twin
     ms = timed(lambda: head(x1), 10)
-    out["lm_head_batch1"] = {"ms": ms, "effective_uncompressed_GBs": 2.0 * V * HIDDEN / (ms * 1e-3) / 1e9}
+    out["lm_head_batch1"] = {"ms": ms, "effective_uncompressed_GBs": 2.0 * VOCAB * HIDDEN / (ms * 1e-3) / 1e9}
+    del head, table
+
+    out["parity"] = parity_table(mods, dense, device)
     return out
+
+
+# ------------------------------------------------------------------------------ whole model
+
+def full_model(rank, world, device, barrier):
+    """BASELINE config 5: the Llama-2-7B architecture with random-init weights from a seed, every linear, the
+    embedding table and the LM head rANS-compressed through the public API (compress_model with fused
+    projections -> compressed_state_dict -> patch_model / patch_model_tensor_parallel), a 512-token prompt
+    and 128 greedy tokens at batch 1 and 8.  Wall-clock tokens/s (the reference's definition,
+    tests/test_rans_pytorch_runtime.py:89-118) of the prompt pass and of the decode steps; parity against the
+    dense bf16 model (procedure of tests/test_full_model_rans.py:227-237): error of the first-step logits,
+    agreement of the argmax over all prompt positions, and the fraction of identical greedy tokens."""
+    import comp_inference_b200 as ci
+    from comp_inference_b200.generation import LlamaGreedyRunner
+    from transformers import LlamaConfig, LlamaForCausalLM
+    t_start = time.perf_counter()
+    cfg = LlamaConfig(hidden_size=HIDDEN, intermediate_size=FFN, num_hidden_layers=32, num_attention_heads=32,
+                      num_key_value_heads=32, vocab_size=VOCAB, rms_norm_eps=1e-5, rope_theta=10000.0,
+                      max_position_embeddings=4096, tie_word_embeddings=False)
+    PROMPT, NEW = 512, 128
+    ids = torch.randint(0, VOCAB, (8, PROMPT), generator=torch.Generator().manual_seed(4001)).to(device)
+
+    def fresh():
+        torch.manual_seed(0)                                    # same weights on every rank and for both models
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(torch.bfloat16)
+        try:
+            with torch.device(device):
+                return LlamaForCausalLM(cfg).eval()
+        finally:
+            torch.set_default_dtype(prev)
+
+    dense = fresh()
+    trace("dense model built")
+    ref = {}
+    if rank == 0:
+        runner = LlamaGreedyRunner(dense, 8, PROMPT + NEW + 8)
+        for B in (1, 8):
+            if B == 1:
+                ref["argmax1"] = runner.prefill(ids[:1], all_logits=True).argmax(-1).cpu()
+            toks, first, t = runner.generate(ids[:B], NEW)
+            ref[f"toks{B}"], ref[f"first{B}"], ref[f"t{B}"] = toks.cpu(), first.float().cpu(), t
+        runner.release()
+        del runner
+        trace("dense reference done")
+    ci.compress_model(dense, tile_height=TILE_H, tile_width=TILE_W, fuse=True, keep_on_device=True)
+    state = ci.compressed_state_dict(dense, to_cpu=False)
+    del dense
+    torch.cuda.empty_cache()
+    n_comp = sum(1 for k in state if k.endswith(".rans_exp_stream"))
+    comp_bytes = sum(v.numel() * v.element_size() for k, v in state.items() if ".rans_" in k)
+    trace(f"compressed {n_comp} tensors")
+    model = fresh()
+    if world == 1:
+        model = ci.prepare_model(ci.patch_model(model, state, default_th=TILE_H, default_tw=TILE_W).to(device))
+    else:
+        model = ci.patch_model_tensor_parallel(model, state, rank, world, default_th=TILE_H, default_tw=TILE_W,
+                                               device=device)
+    del state
+    torch.cuda.empty_cache()
+    kinds = sorted({type(m).__name__ for m in model.modules() if type(m).__name__.startswith("Rans")})
+    trace("compressed model loaded")
+    runner = LlamaGreedyRunner(model, 8, PROMPT + NEW + 8)
+    res = {"model": "Llama-2-7B architecture, 32 layers, random init (seed 0), 6.74 G parameters",
+           "prompt_tokens": PROMPT, "new_tokens": NEW, "tile": [TILE_H, TILE_W], "compressed_tensors": n_comp,
+           "compressed_GB": comp_bytes / 1e9, "modules": kinds,
+           "parallelism": "single GPU" if world == 1 else f"tp{world}: column/row shards, vocabulary-parallel LM head",
+           "decode": "one CUDA graph replay per token (embedding gather, 32 layers, LM head, argmax, KV update)"}
+    for B in (1, 8):
+        argmax = runner.prefill(ids[:1], all_logits=True).argmax(-1).cpu() if B == 1 else None
+        toks, first, t = runner.generate(ids[:B], NEW, barrier=barrier)
+        row = {"prefill_tok_s": t["prefill_tok_s"], "decode_tok_s": t["decode_tok_s"],
+               "decode_ms_per_token": 1e3 * t["decode_s"] / (NEW - 1), "prefill_s": t["prefill_s"]}
+        if rank == 0:
+            r_first = ref[f"first{B}"]
+            row["first_step_logits_rel_err"] = float((first.float().cpu() - r_first).abs().max() / r_first.abs().max())
+            if argmax is not None:
+                row["prompt_argmax_agreement"] = float((argmax == ref["argmax1"]).float().mean())
+            same = (toks.cpu() == ref[f"toks{B}"])
+            row["greedy_tokens_identical"] = float(same.float().mean())
+            row["greedy_identical_prefix"] = float(same.long().cumprod(1).sum(1).float().mean())
+            row["dense_bf16_decode_tok_s"] = ref[f"t{B}"]["decode_tok_s"]
+            row["dense_bf16_prefill_tok_s"] = ref[f"t{B}"]["prefill_tok_s"]
+        res[f"batch{B}"] = row
+        runner.release()
+    ci.check_status()
+    for e in getattr(model, "_ci_exchanges", []):
+        e.check_status()
+    res["setup_s"] = time.perf_counter() - t_start
+    runner.release()
+    del runner
+    if world > 1:
+        ci.close_tensor_parallel(model)
+    del model
+    torch.cuda.empty_cache()
+    return res
 
 
 def kernels_once(args):
@@ -238,6 +494,7 @@ def kernels_once(args):
                                               m.rans_exp_slot_map, (K, N), m.rans_exp_tile_offsets,
                                               m.rans_exp_tile_max_lens, m.tile_k, m.tile_n, m.rans_man_raw)  # k_embedding4
     torch.cuda.synchronize()
+    ci.check_status()
     ref1, ref512 = x1.float() @ W.float(), x512.float() @ W.float()
     print(json.dumps({"kernels_once": True, "decode_bit_exact": bool(torch.equal(w.view(torch.int16), W.view(torch.int16))),
                       "embedding_bit_exact": bool(torch.equal(rows.view(torch.int16), W[ids].view(torch.int16))),
@@ -250,8 +507,10 @@ def cpu_baseline_run(M, steps, warmup):
     from oracle import oracle as O
     cores = O.default_threads()
     layers = []
-    for name, K, N, seed, kind in LAYERS:
-        raw = make_weight_kn(K, N, seed).view(torch.uint16).numpy()
+    for name, members, kind in LAYERS:
+        K = WEIGHTS[members[0]][0]
+        raw = make_fused_kn(members).view(torch.uint16).numpy()
+        N = raw.shape[1]
         r = O.compress_bf16(raw, TILE_H, TILE_W, cores)
         layers.append((name, K, N, r))
     x = {K: torch.randn(M, K, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16)
@@ -281,8 +540,8 @@ def run_reference(args):
             "vs_baseline": None, "dtype": "u8 rANS decode + bf16 x bf16 -> fp32", "data": "synthetic",
             "config": workload_config(args.batch, 1),
             "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
-                             "sample": f"{steps} full steps (7 layers decoded and multiplied per step); the reference "
-                                       "ships no CPU codec, this is the C restatement of its algorithm"},
+                             "sample": f"{steps} full steps (the block's weights decoded and multiplied per step); the "
+                                       "reference ships no CPU codec, this is the C restatement of its algorithm"},
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -290,6 +549,9 @@ def run_reference(args):
 def workload_config(M, world):
     return {"workload": "llama2-7b decoder block, 7 compressed linears, fused decode-GEMV", "batch": M,
             "shapes_out_in": [[4096, 4096]] * 4 + [[11008, 4096]] * 2 + [[4096, 11008]],
+            "launches_per_step": 4,
+            "fused_projections": "q|k|v as one [4096,12288] and gate|up as one [4096,22016] compressed matrix "
+                                 "(rans_compress_qkv_fused / rans_compress_gate_up_fused): 4 launches over the 7 weights",
             "tile": [TILE_H, TILE_W], "weights": "N(0,0.02) bf16, seeded", "activations": "N(0,1) bf16",
             "l2": "inputs larger than L2 (about 290 MB of compressed weights per step)",
             "parallelism": "single GPU" if world == 1 else f"tp{world} (column/row shards of the compressed tiles)"}
@@ -306,58 +568,61 @@ def run_ours(args):
     device = torch.device("cuda", local)
     trace("start")
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")          # plain peer loads and stores only
         dist.init_process_group("nccl", device_id=device)
         trace("process group up")
+    import comp_inference_b200 as ci
     M = args.batch
-    mods, wbytes, notes = build_block(rank, world, device)
+    peak_hbm, peak_tf, src = peaks()
+    mods, wbytes, notes, dense = build_block(rank, world, device, keep_dense=(world == 1 and not args.no_extra))
+    reducer = None
     if world > 1:
         from comp_inference_b200.collective import OneShotAllReduce
         reducer = OneShotAllReduce(capacity=16 * HIDDEN, device=device)
         row_mods = [m for m in mods.values() if hasattr(m, "reducer")]
         for m in row_mods:
             m.reducer = reducer
-            m._fusable = False
-        fuse = reducer.native and not args.no_fuse_exchange
-        if fuse:
-            # one step each way before anything is timed: the fused exchange must reproduce the separate one on
-            # every rank, else all ranks drop it together
-            xt = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(77)).to(torch.bfloat16).to(device)
-            y_sep = block_step(mods, xt, world).float()
-            for m in row_mods:
-                m._fusable = True
-            y_fused = block_step(mods, xt, world).float()
-            torch.cuda.synchronize()
-            from comp_inference_b200 import _lib as _cl
-            good = (float((y_fused - y_sep).abs().max()) <= 3e-2 * max(float(y_sep.abs().max()), 1e-6)
-                    and reducer.status() == 0 and _cl.kernel_status(device) == 0)
-            verdict = torch.tensor([1 if good else 0], device=device, dtype=torch.int32)
-            dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
-            fuse = bool(verdict.item())
-            for m in row_mods:
-                m._fusable = fuse
-            if not fuse:
-                notes.append("fused exchange failed its check against the separate one: not used")
-        how = "fused into the row-parallel GEMV" if fuse else "one-shot kernel behind the GEMV"
+            m.fuse_exchange = not args.no_fuse_exchange
+            m.prepare()                                         # collective: the group's verdict per layer
+        fused = [m._fusable for m in row_mods]
+        how = ("fused into the row-parallel GEMV" if all(fused) else
+               "one-shot kernel behind the GEMV" if not any(fused) else "fused in some layers, one-shot kernel in others")
         notes.append(f"activation all-reduce over peer memory, {how}" if reducer.native
                      else f"activation all-reduce: NCCL ({reducer.why})")
+    for m in mods.values():
+        if not hasattr(m, "reducer"):
+            m.prepare()
 
     gen = torch.Generator().manual_seed(2000 + M)
     x_host = torch.randn(M, HIDDEN, generator=gen).to(torch.bfloat16).pin_memory()
     x_dev = x_host.to(device)
     y_host = torch.empty(M, HIDDEN, dtype=torch.bfloat16).pin_memory()
 
+    # ---- N > 1: the N-rank result against the unsharded block on rank 0 ------------------------
+    tp_err = None
+    if world > 1:
+        y_tp = block_step(mods, x_dev).float()
+        torch.cuda.synchronize()
+        if rank == 0:
+            full, _, _, _ = build_block(0, 1, device)
+            y_full = block_step(full, x_dev).float()
+            tp_err = float((y_tp - y_full).abs().max() / y_full.abs().max())
+            del full
+            torch.cuda.empty_cache()
+        dist.barrier()
+
     # ---- device-resident: one CUDA graph per step -------------------------------------------
     for _ in range(3):
-        y = block_step(mods, x_dev, world)
+        block_step(mods, x_dev)
     torch.cuda.synchronize()
     trace("eager warm-up done")
     side = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
-        block_step(mods, x_dev, world)
+        block_step(mods, x_dev)
         torch.cuda.synchronize()
         with torch.cuda.graph(graph, stream=side):
-            y_graph = block_step(mods, x_dev, world)
+            y_graph = block_step(mods, x_dev)
     torch.cuda.synchronize()
     trace("graph captured")
 
@@ -366,118 +631,161 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed_region(fn):
+        """`steps` calls bracketed by barriers, REPEATS times; the per-step milliseconds of every repeat (max
+        over ranks)."""
+        out = []
+        for _ in range(REPEATS):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            barrier()
+            out.append(e0.elapsed_time(e1) / args.steps)
+        if world > 1:
+            t = torch.tensor(out, device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out = t.tolist()
+        return out
+
     for _ in range(max(args.warmup, 3)):
         graph.replay()
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
         time.sleep(0.3)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    barrier()
-    dev_ms = e0.elapsed_time(e1) / args.steps
-    trace(f"device loop done {dev_ms:.3f} ms/step")
+    dev_runs = timed_region(graph.replay)
+    dev_ms = statistics.median(dev_runs)
+    trace(f"device loop done {dev_ms:.4f} ms/step")
 
     # ---- end to end: public module API, host buffers, copies inside the timed region ------
     # What a serving loop does per token: the step (copy of the pinned host activations to the device, the
-    # seven module calls, copy of the result to pinned host memory) is captured once with torch.cuda.graph
+    # module calls, copy of the result to pinned host memory) is captured once with torch.cuda.graph
     # and replayed; the caller waits for the result before the next token.
     x_in = torch.empty_like(x_dev)
     e2e_graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
         x_in.copy_(x_host, non_blocking=True)
-        y_host.copy_(block_step(mods, x_in, world), non_blocking=True)
+        y_host.copy_(block_step(mods, x_in), non_blocking=True)
         torch.cuda.synchronize()
         with torch.cuda.graph(e2e_graph, stream=side):
             x_in.copy_(x_host, non_blocking=True)
-            y_e2e = block_step(mods, x_in, world)
+            y_e2e = block_step(mods, x_in)
             y_host.copy_(y_e2e, non_blocking=True)
     torch.cuda.synchronize()
+
+    def e2e_step():
+        e2e_graph.replay()
+        torch.cuda.current_stream().synchronize()              # the caller needs the result before the next token
+
     for _ in range(max(args.warmup, 3)):
-        e2e_graph.replay()
-        torch.cuda.current_stream().synchronize()
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for _ in range(args.steps):
-        e2e_graph.replay()
-        torch.cuda.current_stream().synchronize()          # the caller needs the result before the next token
-    e3.record()
-    barrier()
-    e2e_ms = e2.elapsed_time(e3) / args.steps
+        e2e_step()
+    e2e_runs = timed_region(e2e_step)
+    e2e_ms = statistics.median(e2e_runs)
+    time.sleep(0.2)
     trace("e2e loop done")
     clocks = sampler.stop() if sampler else None
 
     if world > 1:
-        t = torch.tensor([dev_ms, e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = t.tolist()
         wb = torch.tensor([float(wbytes)], device=device, dtype=torch.float64)
         dist.all_reduce(wb)
         wbytes_total = wb.item()
     else:
         wbytes_total = float(wbytes)
 
-    # parity spot check of the graph's result against a dense matmul on decoded weights happens in tests;
-    # here only sanity: finite output
     assert torch.isfinite(y_graph.float()).all() and torch.equal(y_host, y_graph.cpu())
+    ci.check_status()                                           # raises if any kernel reported an error
+    if reducer is not None:
+        reducer.check_status()
+    routes = block_routes(mods, M)
 
+    extra = {}
+    if world == 1 and not args.no_extra:
+        extra = secondary_metrics(mods, dense, device, peak_hbm, peak_tf, src)
+        trace("secondary metrics done")
+    del dense
+    # the block's graphs refer to the group's communicators; drop them before the model run sets up its own
+    del graph, y_graph, e2e_graph, y_e2e
+    for m in mods.values():
+        m.reducer = None
+    del mods
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    if reducer is not None:
+        reducer.close()
+    if not args.no_full_model:
+        try:
+            extra["full_model"] = full_model(rank, world, device, barrier if world > 1 else None)
+        except Exception as e:                                  # the headline line must still be printed
+            extra["full_model"] = {"error": f"{type(e).__name__}: {e}"}
+            if world > 1:
+                raise
+        trace("full model done")
+
+    failed = tp_err is not None and tp_err > 1e-2
     if rank == 0:
-        peak, src = peaks()
         # algorithmic bytes of one step on one GPU: compressed weights + activations in + results out
-        act = sum(2 * M * (K + N) for _, K, N, _, _ in LAYERS)
+        act = sum(2 * M * (WEIGHTS[members[0]][0] + sum(WEIGHTS[n][1] for n in members)) for _, members, _ in LAYERS)
         algo = wbytes_total / world + act / world
         launches = len(LAYERS)
         per_launch_s = dev_ms * 1e-3 / launches               # collectives included at N > 1 (noted in config)
         achieved = algo / launches / per_launch_s / 1e9
         traffic = (wbytes_total / world / launches) * (NCU_TRAFFIC_4096 / NCU_BYTES_4096)
         line = {"metric": METRIC, "value": M / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dev_ms, "higher_is_better": True,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dev_ms,
+                "repeats": REPEATS, "ms_per_step_min_max": [min(dev_runs), max(dev_runs)],
+                "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "u8 rANS decode + bf16 x bf16 -> fp32 (mma.sync)",
                 "data": "synthetic", "config": workload_config(M, world),
                 "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+                        "ms_per_step_min_max": [min(e2e_runs), max(e2e_runs)],
                         "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
                 "gpu_launches": launches * args.steps,
-                "roofline": {"bound": "hbm", "kernel": "k_linear_mma4", "achieved": achieved, "peak": peak,
-                             "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {src}",
+                "roofline": {"bound": "hbm", "kernel": " + ".join(routes), "achieved": achieved, "peak": peak_hbm,
+                             "unit": "GB/s", "frac": achieved / peak_hbm, "peak_source": f"of {src}",
                              "frac_of_nominal_8TBs": achieved / 8000.0, "traffic": traffic,
+                             "traffic_source": NCU_CAPTURE,
                              "algorithmic_bytes_per_launch": algo / launches,
-                             "effective_uncompressed_GBs": sum(2 * K * N for _, K, N, _, _ in LAYERS) / world
+                             "effective_uncompressed_GBs": sum(2 * K * N for K, N, _ in WEIGHTS.values()) / world
                              / (dev_ms * 1e-3) / 1e9},
                 "clocks": clocks, "notes": notes}
-        if world == 1:
-            line["extra"] = secondary_metrics(mods, device)
+        if tp_err is not None:
+            extra["tp_parity_rel_err"] = tp_err
+        if extra:
+            line["extra"] = extra
         if world == 1 and not args.no_cpu:
             val, ms, cores = cpu_baseline_run(M, 1, 1)
             line["cpu_baseline"] = {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
-                                    "sample": "1 full step after 1 warm-up step (7 layers decoded and multiplied), "
-                                              "CPU restatement of the reference algorithm, all host cores"}
+                                    "sample": "1 full step after 1 warm-up step (the block's weights decoded and "
+                                              "multiplied), CPU restatement of the reference algorithm, all host cores"}
         print(json.dumps(line))
+        if failed:
+            print(f"tensor-parallel result differs from the unsharded block by {tp_err:.3e} (> 1e-2)", file=sys.stderr)
     if world > 1:
-        # The captured graph still refers to the NCCL communicator; tearing the process group down while
-        # it exists blocked for minutes on the 2-GPU box.  Drop the graph, line the ranks up, and leave
-        # communicator clean-up to process exit.
+        # Communicator clean-up is left to process exit: tearing the process group down after graphs that
+        # referred to it blocked for minutes on a 2-GPU box.  All graphs and peer buffers are gone by now.
         trace("shutting down")
-        del graph, y_graph, e2e_graph, y_e2e
         torch.cuda.synchronize()
         dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(1 if failed else 0)
+    if failed:
+        sys.exit(1)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary metrics (N = 1)")
+    ap.add_argument("--no-full-model", action="store_true", help="skip the whole-model run")
     ap.add_argument("--no-fuse-exchange", action="store_true",
                     help="N > 1: all-reduce with the one-shot kernel behind the row-parallel GEMV instead of inside it")
     ap.add_argument("--kernels-once", action="store_true",

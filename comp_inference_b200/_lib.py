@@ -68,6 +68,7 @@ SIGNATURES = {
     "ci_linear_workspace_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "ci_linear": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _V, C.c_size_t,
                             C.c_uint32, _S]),
+    "ci_linear_route": (C.c_int, [C.POINTER(TiledWeight), C.c_uint32]),
     "ci_linear_static_max_bytes": (C.c_size_t, []),
     "ci_linear_static": (C.c_int, [C.POINTER(TiledWeight), _V, C.c_int64, C.c_uint32, _V, _V, C.c_int64, _S]),
     "ci_linear_static_status": (C.c_int, [u32p, C.c_int, _S]),

@@ -142,8 +142,8 @@ class OneShotAllReduce(_PeerExchange):
         M = x2.shape[0]
         from . import ops
         lib = _lib.load()
-        if x2.data_ptr() % 16 or x2.stride(0) != x2.shape[1]:
-            x2 = x2.contiguous().clone()                        # the kernel reads 8-byte quads of dense rows
+        if x2.data_ptr() % 8 or x2.stride(0) % 4:
+            x2 = x2.contiguous().clone()                        # the kernel reads the rows as aligned 8-byte quads
         y = torch.empty((M, n_out), device=x2.device, dtype=torch.bfloat16)
         ws = _lib.workspace(x2.device, lib.ci_linear_workspace_bytes(M, n_out, w.K, w.tile_h))
         b = ops._bias(bias, n_out)

@@ -128,9 +128,11 @@ def compress_weight_cuda(weight_kn: torch.Tensor, tile_height=1024, tile_width=3
 
 
 def rans_compress_module_weight_bf16(module: nn.Module, skip_mantissa=True, tile_height=1024, tile_width=32,
-                                     transpose_weight=True, uncoalesced_interleaving=False) -> None:
+                                     transpose_weight=True, uncoalesced_interleaving=False,
+                                     keep_on_device=False) -> None:
     """Replaces module.weight by the compressed attributes the reference sets
-    (comp_inference/comp_inference.py:344-502); attribute tensors are CPU tensors, as there."""
+    (comp_inference/comp_inference.py:344-502); attribute tensors are CPU tensors, as there, unless
+    ``keep_on_device`` (not in the reference) asks to leave them on the GPU that produced them."""
     if not hasattr(module, "weight"):
         return
     if module.weight.dtype != torch.bfloat16:
@@ -159,9 +161,11 @@ def rans_compress_module_weight_bf16(module: nn.Module, skip_mantissa=True, tile
     module.mantissa_freqs, module.mantissa_cdf = _normalize(mhist)
     mgr = ccore.RansManager(module.expanded_size)
     if uncoalesced_interleaving:
-        r = mgr.compress_tiled_uncoalesced(exp, module.exponent_freqs, module.exponent_cdf, th, tw)
+        r = mgr.compress_tiled_uncoalesced(exp, module.exponent_freqs, module.exponent_cdf, th, tw,
+                                           _keep_on_device=keep_on_device)
     else:
-        r = mgr.compress_tiled(exp, module.exponent_freqs, module.exponent_cdf, th, tw)
+        r = mgr.compress_tiled(exp, module.exponent_freqs, module.exponent_cdf, th, tw,
+                               _keep_on_device=keep_on_device)
     if r.success:
         module.exponent_compressed_weight = r.stream
         module.exponent_states = r.states
@@ -180,13 +184,13 @@ def rans_compress_module_weight_bf16(module: nn.Module, skip_mantissa=True, tile
             module.exponent_tile_offsets = r.tile_offsets
             module.exponent_tile_max_lens = r.tile_max_lens
     else:
-        module.exponent_raw = exp.cpu()
-    module.mantissa_raw = man.cpu()
+        module.exponent_raw = exp if keep_on_device else exp.cpu()
+    module.mantissa_raw = man if keep_on_device else man.cpu()
     module.compressed = "rans_bfloat16"
     del module.weight
 
 
-def _fused(modules, tile_height, tile_width, uncoalesced_interleaving):
+def _fused(modules, tile_height, tile_width, uncoalesced_interleaving, keep_on_device=False):
     ws = [m.weight for m in modules]
     assert all(w.dtype == torch.bfloat16 for w in ws)
     assert all(w.shape[1] == ws[0].shape[1] for w in ws)
@@ -194,40 +198,41 @@ def _fused(modules, tile_height, tile_width, uncoalesced_interleaving):
     lin = nn.Linear(fused.shape[1], fused.shape[0], bias=False, device=fused.device, dtype=fused.dtype)
     lin.weight = nn.Parameter(fused, requires_grad=False)
     rans_compress_module_weight_bf16(lin, tile_height=tile_height, tile_width=tile_width,
-                                     uncoalesced_interleaving=uncoalesced_interleaving)
+                                     uncoalesced_interleaving=uncoalesced_interleaving, keep_on_device=keep_on_device)
     return lin
 
 
 def rans_compress_qkv_fused(self_attn_module: nn.Module, tile_height=1024, tile_width=32,
-                            uncoalesced_interleaving=False):
+                            uncoalesced_interleaving=False, keep_on_device=False):
     """q/k/v concatenated along the output dimension and compressed as one tensor, attached under the
     name q_proj (comp_inference/comp_inference.py:242-292)."""
     a = self_attn_module
-    a.q_proj = _fused([a.q_proj, a.k_proj, a.v_proj], tile_height, tile_width, uncoalesced_interleaving)
+    a.q_proj = _fused([a.q_proj, a.k_proj, a.v_proj], tile_height, tile_width, uncoalesced_interleaving, keep_on_device)
     a.qkv_fused = True
     del a.k_proj
     del a.v_proj
 
 
 def rans_compress_gate_up_fused(ffn_module: nn.Module, tile_height=1024, tile_width=32,
-                                uncoalesced_interleaving=False):
+                                uncoalesced_interleaving=False, keep_on_device=False):
     """gate/up concatenated and compressed as one tensor, attached as gate_proj
     (comp_inference/comp_inference.py:295-341)."""
     f = ffn_module
-    f.gate_proj = _fused([f.gate_proj, f.up_proj], tile_height, tile_width, uncoalesced_interleaving)
+    f.gate_proj = _fused([f.gate_proj, f.up_proj], tile_height, tile_width, uncoalesced_interleaving, keep_on_device)
     f.gate_up_fused = True
     del f.up_proj
 
 
 def rans_compress_module_weight(module: nn.Module, tile_height=1024, tile_width=32, transpose_weight=True,
-                                uncoalesced_interleaving=False) -> None:
+                                uncoalesced_interleaving=False, keep_on_device=False) -> None:
     """Dispatcher of comp_inference/comp_inference.py:548-570 (the int8 branch is broken upstream and not offered)."""
     if not hasattr(module, "weight"):
         return
     if module.weight.dtype == torch.bfloat16:
         rans_compress_module_weight_bf16(module, tile_height=tile_height, tile_width=tile_width,
                                          transpose_weight=transpose_weight,
-                                         uncoalesced_interleaving=uncoalesced_interleaving)
+                                         uncoalesced_interleaving=uncoalesced_interleaving,
+                                         keep_on_device=keep_on_device)
     else:
         print(f"Module weight dtype is {module.weight.dtype}, not supported for RANS compression. Skipping.")
 

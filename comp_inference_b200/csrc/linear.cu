@@ -528,6 +528,24 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t ldx, uint32
     return linear_impl(w, d_x, ldx, M, d_bias, d_y, ldy, d_ws, ws_bytes, split_k, nullptr, stream);
 }
 
+int ci_linear_route(const ci_tiled_weight *w, uint32_t M) {
+    int rc = check_weight(w, true);
+    if (rc) return rc;
+    if (M == 0) return 0;
+    if (M > 16) return 3;                                       // tcgen05 decode-GEMM (given a workspace)
+    LinArgs a = base_args(w);
+    a.M = M;
+    a.ldx = w->K;
+    a.ldy = w->N;
+    a.dry_run = 1;
+    rc = launch_linear_mma4(a, w->max_tile_len, nullptr);
+    if (rc == CI_OK) return 2;
+    if (rc < 0) return rc;
+    rc = launch_linear_mma(a, w->max_tile_len, nullptr);
+    if (rc == CI_OK) return 1;
+    return rc < 0 ? rc : 0;
+}
+
 size_t ci_linear_allreduce_counter_bytes(void) { return 2 * sizeof(uint32_t); }
 
 int ci_linear_allreduce_qualifies(const ci_tiled_weight *w, uint32_t M) {

@@ -90,6 +90,8 @@ def _linear_call(w, x2, M, n_out, bias, out, split_k, transposed):
     if y.dtype != torch.bfloat16 or y.stride(1) != 1:
         raise RuntimeError("out must be a bfloat16 tensor with unit inner stride")
     nbytes = lib.ci_linear_workspace_bytes(M, n_out, 0 if transposed else w.K, 0 if transposed else w.tile_h)
+    if M > 16 and not transposed and split_k > 1:               # an explicit split-K of the prefill GEMM: room for its partials
+        nbytes = max(nbytes, (1 << 14) + min(int(split_k), 8) * M * n_out * 4)
     ws = _lib.workspace(dev, nbytes)
     b = _bias(bias, n_out)
     if transposed:

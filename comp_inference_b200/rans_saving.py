@@ -27,14 +27,17 @@ def _bf16_linear(m):
     return isinstance(m, nn.Linear) and m.weight.dtype == torch.bfloat16 and m.bias is None
 
 
-def compress_model(model, tile_height=1024, tile_width=32, layer_tiles=None, tied_lm_head=None, fuse=False):
+def compress_model(model, tile_height=1024, tile_width=32, layer_tiles=None, tied_lm_head=None, fuse=False,
+                   keep_on_device=False):
     """Compresses every bf16 nn.Linear / nn.Embedding of a Hugging Face causal LM in place, the way the
     reference's end-to-end script does (tests/test_full_model_rans.py:75-130): linears are stored
     transposed ([in, out]); the embedding table and the LM head keep their [vocab, hidden] layout.
     ``layer_tiles`` maps a module name to (tile_height, tile_width) for per-layer tile sizes.
     ``fuse``: q/k/v and gate/up projections are concatenated and compressed as one tensor each
     (rans_compress_qkv_fused / rans_compress_gate_up_fused, as the reference's script does with its
-    fuse option, tests/test_full_model_rans.py:97-118); save such a model with ``fuse=True``."""
+    fuse option, tests/test_full_model_rans.py:97-118); save such a model with ``fuse=True``.
+    ``keep_on_device``: leave the compressed tensors on the GPU instead of moving them to the host as the
+    reference does (for a model that is patched and run right away, compressed_state_dict(to_cpu=False))."""
     layer_tiles = layer_tiles or {}
     if tied_lm_head is None:
         tied_lm_head = bool(getattr(model.config, "tie_word_embeddings", False))
@@ -42,10 +45,10 @@ def compress_model(model, tile_height=1024, tile_width=32, layer_tiles=None, tie
         for name, module in list(model.named_modules()):
             if all(_bf16_linear(getattr(module, a, None)) for a in ("q_proj", "k_proj", "v_proj")):
                 th, tw = layer_tiles.get(name + ".q_proj", (tile_height, tile_width))
-                ci.rans_compress_qkv_fused(module, tile_height=th, tile_width=tw)
+                ci.rans_compress_qkv_fused(module, tile_height=th, tile_width=tw, keep_on_device=keep_on_device)
             if all(_bf16_linear(getattr(module, a, None)) for a in ("gate_proj", "up_proj")):
                 th, tw = layer_tiles.get(name + ".gate_proj", (tile_height, tile_width))
-                ci.rans_compress_gate_up_fused(module, tile_height=th, tile_width=tw)
+                ci.rans_compress_gate_up_fused(module, tile_height=th, tile_width=tw, keep_on_device=keep_on_device)
     for name, module in list(model.named_modules()):
         if getattr(module, "compressed", None) is not None:
             continue
@@ -56,19 +59,21 @@ def compress_model(model, tile_height=1024, tile_width=32, layer_tiles=None, tie
             continue
         th, tw = layer_tiles.get(name, (tile_height, tile_width))
         keep_layout = is_head or isinstance(module, nn.Embedding)
-        ci.rans_compress_module_weight(module, tile_height=th, tile_width=tw, transpose_weight=not keep_layout)
+        ci.rans_compress_module_weight(module, tile_height=th, tile_width=tw, transpose_weight=not keep_layout,
+                                       keep_on_device=keep_on_device)
     return model
 
 
-def _save_rans_attributes(tensors, base, module):
+def _save_rans_attributes(tensors, base, module, to_cpu=True):
     """One module's tensors under the reference's key names (rans_saving.py:352-481)."""
-    u32 = lambda t: t.cpu().view(torch.uint32) if t.dtype == torch.int32 else t.cpu().to(torch.uint32)
+    mv = (lambda t: t.cpu()) if to_cpu else (lambda t: t)
+    u32 = lambda t: mv(t).view(torch.uint32) if t.dtype == torch.int32 else mv(t).to(torch.uint32)
     dense = bool(getattr(module, "exponent_uncoalesced_interleaving", False))
     if hasattr(module, "exponent_compressed_weight"):
-        tensors[base + "rans_exp_stream"] = module.exponent_compressed_weight.cpu().to(torch.uint8)
+        tensors[base + "rans_exp_stream"] = mv(module.exponent_compressed_weight).to(torch.uint8)
         tensors[base + "rans_exp_states"] = u32(module.exponent_states)
         tensors[base + "rans_exp_tables"] = u32(module.exponent_tables)
-        tensors[base + "rans_exp_slot_map"] = module.exponent_slot_map.cpu().to(torch.uint8)
+        tensors[base + "rans_exp_slot_map"] = mv(module.exponent_slot_map).to(torch.uint8)
         if dense:
             tensors[base + "rans_exp_stream_offsets"] = u32(module.exponent_stream_offsets)
             tensors[base + "rans_exp_sizes"] = u32(module.exponent_output_sizes)
@@ -77,32 +82,34 @@ def _save_rans_attributes(tensors, base, module):
             tensors[base + "rans_exp_tile_max_lens"] = u32(module.exponent_tile_max_lens)
         exp_compressed, exp_streams = 1, int(module.exponent_num_streams)
     else:
-        tensors[base + "rans_exp_raw"] = module.exponent_raw.cpu()
+        tensors[base + "rans_exp_raw"] = mv(module.exponent_raw)
         exp_compressed, exp_streams = 0, 0
-    tensors[base + "rans_man_raw"] = module.mantissa_raw.cpu().to(torch.uint8)
+    tensors[base + "rans_man_raw"] = mv(module.mantissa_raw).to(torch.uint8)
     shape = list(getattr(module, "input_shape", []))
     info = [1, int(module.expanded_size), exp_compressed, exp_streams, 0, 0, len(shape),
             int(getattr(module, "exponent_num_tiles_n", 0)), int(getattr(module, "exponent_num_tiles_k", 0)),
             int(getattr(module, "exponent_tile_height", 0)), int(getattr(module, "exponent_tile_width", 0))] + shape
     tensors[base + "rans_info"] = torch.tensor(info, dtype=torch.int32)
     if getattr(module, "bias", None) is not None:
-        tensors[base + "bias"] = module.bias.detach().cpu()
+        tensors[base + "bias"] = mv(module.bias.detach())
 
 
-def compressed_state_dict(model, tied_lm_head: bool = False):
-    """The tensors pack_and_save_tensors would write, as a dict (CPU tensors): what patch_model and
-    patch_model_tensor_parallel take, without the round trip through a file."""
+def compressed_state_dict(model, tied_lm_head: bool = False, to_cpu: bool = True):
+    """The tensors pack_and_save_tensors would write, as a dict: what patch_model and
+    patch_model_tensor_parallel take, without the round trip through a file.  CPU tensors like a loaded
+    package, or -- ``to_cpu=False`` -- wherever the compressed attributes live (compress_model(keep_on_device=True))."""
+    mv = (lambda t: t.cpu()) if to_cpu else (lambda t: t)
     tensors, handled = {}, set()
     if tied_lm_head:
         handled.update({"lm_head.weight", "model.lm_head.weight"})
     for name, module in model.named_modules():
         if getattr(module, "compressed", None) == "rans_bfloat16":
-            _save_rans_attributes(tensors, name + ".", module)
+            _save_rans_attributes(tensors, name + ".", module, to_cpu)
             handled.add(name + ".weight")
             handled.add(name + ".bias")
     for pname, param in model.named_parameters():
         if pname not in handled:
-            tensors[pname] = param.detach().cpu().contiguous()
+            tensors[pname] = mv(param.detach()).contiguous()
     return tensors
 
 

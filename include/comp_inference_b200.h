@@ -219,6 +219,12 @@ int ci_linear(const ci_tiled_weight *w, const uint16_t *d_x, int64_t x_row_strid
               uint16_t *d_y, int64_t y_row_stride, void *d_workspace, size_t workspace_bytes, uint32_t split_k,
               ci_stream_t stream);
 
+/* Which kernel ci_linear (split_k = 0, aligned buffers, a workspace) runs for this weight and M rows:
+ * 0 = generic split-K kernel, 1 = staged two-streams-per-lane kernel (k_linear_mma), 2 = register-direct
+ * four-streams-per-lane kernel (k_linear_mma4), 3 = tcgen05 decode-GEMM (k_linear_gemm).  Launches nothing;
+ * benchmarks label their roofline with it. */
+int ci_linear_route(const ci_tiled_weight *w, uint32_t M);
+
 /* ci_linear for callers that cannot allocate device memory (no counterpart in the reference).
  *
  * Meant for hosts that are forbidden to call cudaMalloc or any allocating routine while the model

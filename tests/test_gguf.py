@@ -139,3 +139,45 @@ def test_raw_exponent_plane_module(oracle, tmp_path):
     assert np.array_equal(got["blk.0.ffn_down.rans_exp_raw"].reshape(160, 96), e)
     assert np.array_equal(oracle.merge_bf16(got["blk.0.ffn_down.rans_exp_raw"].reshape(160, 96),
                                             got["blk.0.ffn_down.rans_man_raw"].reshape(160, 96)), bits(w))
+
+
+@pytest.mark.gpu
+def test_gpu_compressed_module_through_a_file_and_back(tmp_path):
+    """The whole way on the GPU path: modules compressed by the CUDA encoder -> GGUF file -> read_rans_gguf ->
+    CUDA decoder, bit-exact, with nothing but the file's contents."""
+    import comp_inference_b200 as ci
+    model = _Model()
+    blk = model.model.layers[0]
+    wq, wd = make_weight(160, 96, 21), make_weight(96, 160, 22)          # HF layout [out, in]
+    with torch.no_grad():
+        blk.self_attn.q_proj.weight.copy_(wq)
+        blk.mlp.down_proj.weight.copy_(wd)
+    ci.rans_compress_module_weight(blk.self_attn.q_proj, tile_height=64, tile_width=32)
+    ci.rans_compress_module_weight(blk.mlp.down_proj, tile_height=128, tile_width=16)
+    path = str(tmp_path / "gpu.gguf")
+    rans_gguf.save_rans_model_gguf(model, None, path, arch="llama")
+    got = rans_gguf.read_rans_gguf(path)
+    dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).view(dt).cuda()
+    for base, w in (("blk.0.attn_q", wq), ("blk.0.ffn_down", wd)):
+        info = got[base + ".rans_info"].tolist()
+        tn, tk, th, tw = info[7:11]
+        K, N = info[11:13]
+        out = ci.rans_decompress_bf16(dev(got[base + ".rans_exp_stream"], torch.uint8),
+                                      dev(got[base + ".rans_exp_states"].view(np.int32), torch.int32),
+                                      dev(got[base + ".rans_exp_tables"].view(np.int32), torch.int32),
+                                      dev(got[base + ".rans_exp_slot_map"], torch.uint8), (K, N),
+                                      dev(got[base + ".rans_exp_tile_offsets"].view(np.int32), torch.int32),
+                                      dev(got[base + ".rans_exp_tile_max_lens"].view(np.int32), torch.int32), th, tw,
+                                      dev(got[base + ".rans_man_raw"], torch.uint8))
+        assert torch.equal(out.cpu().view(torch.uint16), w.t().contiguous().view(torch.uint16))     # stored [in, out]
+        # and the fused linear straight from the file's arrays
+        x = torch.randn(2, K, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+        y = ci.fused_rans_linear_triton(x, dev(got[base + ".rans_exp_stream"], torch.uint8),
+                                        dev(got[base + ".rans_exp_states"].view(np.int32), torch.int32),
+                                        dev(got[base + ".rans_exp_tables"].view(np.int32), torch.int32),
+                                        dev(got[base + ".rans_exp_slot_map"], torch.uint8), (K, N),
+                                        dev(got[base + ".rans_exp_tile_offsets"].view(np.int32), torch.int32),
+                                        dev(got[base + ".rans_exp_tile_max_lens"].view(np.int32), torch.int32), th, tw,
+                                        dev(got[base + ".rans_man_raw"], torch.uint8), SPLIT_K=0)
+        ref = x.float().cpu() @ w.t().float()
+        assert float((y.float().cpu() - ref).abs().max() / ref.abs().max()) <= 1e-2

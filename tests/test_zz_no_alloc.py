@@ -45,11 +45,24 @@ def test_static_scratch_matches_workspace_version(K, N, th, M):
     _call(lib, lib.ci_linear, w, x, want, ws)
     ref = x.float() @ W.float()
     assert float((want.float() - ref).abs().max() / ref.abs().max()) <= 1e-2
+    got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _call(lib, lib.ci_linear_static, w, x, got)          # first call: kernel code is loaded, the array's address looked up
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.uint16), want.view(torch.uint16))
     for _ in range(2):                                   # twice in a row: the shared array is reused as it was left
-        got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         _call(lib, lib.ci_linear_static, w, x, got)
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        # the property the entry point exists for: the call itself takes no device memory
+        assert free_after == free_before, (free_before, free_after)
         assert torch.equal(got.view(torch.uint16), want.view(torch.uint16))
+    # nothing went wrong inside the built-in array either: its status word (which the per-call clearing leaves
+    # alone) is zero
+    code = C.c_uint32(99)
+    assert lib.ci_linear_static_status(C.byref(code), 0, _lib.stream()) == 0 and code.value == 0
 
 
 def test_static_scratch_rejects_what_does_not_fit():
