@@ -514,6 +514,86 @@ def full_model(rank, world, device, barrier):
     return res
 
 
+def reference_triton(args):
+    """The reference's own GPU path on this GPU, for the column next to ours: its Python package as installed
+    under baseline/_ref (``pip install --target``; git-ignored, so present only where that install was made),
+    its CUDA encoder and its Triton fused linear (comp_inference/linear_triton.py:229-314) through its public
+    functions, on the block's seven weights at batch 1.  Runs in a process of its own and prints one JSON
+    line; the caller treats any failure as "unavailable"."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "comp_inference")):
+        print(json.dumps({"unavailable": "the reference package is not installed under baseline/_ref"}))
+        return
+    sys.path.insert(0, ref_dir)
+    import contextlib
+    import io
+    torch.cuda.set_device(0)
+    with contextlib.redirect_stdout(io.StringIO()):
+        import comp_inference as ref                            # the reference prints on import and on every call
+    out = {"package": "reference installed from its sources (pip --target baseline/_ref), stock code path"}
+    x_cache = {}
+
+    def run(tile_h, split_k):
+        mods = {}
+        fd = os.dup(1)
+        devnull = os.open(os.devnull, os.O_WRONLY)
+        os.dup2(devnull, 1)                                     # the extension prints from C++
+        try:
+            for name, (K, N, seed) in WEIGHTS.items():
+                lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+                lin.weight = torch.nn.Parameter(make_weight_kn(K, N, seed).t().contiguous(), requires_grad=False)
+                ref.rans_compress_module_weight(lin, tile_height=tile_h, tile_width=TILE_W, transpose_weight=True)
+                mods[name] = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in vars(lin).items()
+                              if k.startswith("exponent_") or k in ("mantissa_raw", "input_shape")}
+        finally:
+            os.dup2(fd, 1)
+            os.close(devnull)
+            os.close(fd)
+
+        def call(m, x):
+            return ref.fused_rans_linear_triton(
+                x, m["exponent_compressed_weight"], m["exponent_states"], m["exponent_tables"], m["exponent_slot_map"],
+                tuple(m["input_shape"]), m["exponent_tile_offsets"], m["exponent_tile_max_lens"],
+                m["exponent_tile_height"], m["exponent_tile_width"], m["mantissa_raw"], SPLIT_K=split_k)
+
+        def step():
+            for name, (K, N, seed) in WEIGHTS.items():
+                if K not in x_cache:
+                    x_cache[K] = torch.randn(1, K, generator=torch.Generator().manual_seed(2001)).to(torch.bfloat16).cuda()
+                call(mods[name], x_cache[K])
+
+        step()                                                  # Triton compiles here
+        torch.cuda.synchronize()
+        # parity of the reference's own kernel against a dense matmul, for the record
+        K, N, seed = WEIGHTS["q_proj"]
+        y = call(mods["q_proj"], x_cache[K]).float()
+        want = x_cache[K].float() @ make_weight_kn(K, N, seed).cuda().float()
+        ms = timed(step, 20, warm=3)
+        return {"ms_per_block_7_launches": ms, "tok_s": 1.0 / (ms * 1e-3),
+                "q_proj_rel_err": float((y - want).abs().max() / want.abs().max())}
+
+    for label, th, sk in (("default_tile_1024x32_split_k8", 1024, 8), ("tile_128x32_split_k8", TILE_H, 8),
+                          ("tile_128x32_split_k1", TILE_H, 1)):
+        try:
+            out[label] = run(th, sk)
+        except Exception as e:
+            out[label] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    print(json.dumps(out))
+
+
+def reference_triton_subprocess():
+    """Runs reference_triton() in a child process (its Triton JIT and its prints stay out of this one)."""
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--reference-triton"], capture_output=True,
+                           text=True, timeout=600)
+        for line in reversed(r.stdout.strip().splitlines()):
+            if line.startswith("{"):
+                return json.loads(line)
+        return {"unavailable": f"no result (exit code {r.returncode}): {r.stderr.strip()[-300:]}"}
+    except Exception as e:
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+
+
 def kernels_once(args):
     """One small invocation of each hot kernel on one 4096x4096 weight (24 MB compressed, nothing else resident):
     the case the ncu captures summarised under profiles/ are taken on.  Prints parity figures, no timing."""
@@ -748,6 +828,8 @@ def run_ours(args):
     if world == 1 and not args.no_extra:
         extra = secondary_metrics(mods, dense, device, peak_hbm, peak_tf, src)
         trace("secondary metrics done")
+        extra["reference_triton_b200"] = reference_triton_subprocess()
+        trace("reference Triton leg done")
     del dense
     # the block's graphs refer to the group's communicators; drop them before the model run sets up its own
     del graph, y_graph, e2e_graph, y_e2e
@@ -831,10 +913,14 @@ def main():
     ap.add_argument("--no-full-model", action="store_true", help="skip the whole-model run")
     ap.add_argument("--no-fuse-exchange", action="store_true",
                     help="N > 1: all-reduce with the one-shot kernel behind the row-parallel GEMV instead of inside it")
+    ap.add_argument("--reference-triton", action="store_true",
+                    help="time the reference's own Triton fused linear from baseline/_ref (if installed) and exit")
     ap.add_argument("--kernels-once", action="store_true",
                     help="run each hot kernel three times on one 4096x4096 weight and exit (the ncu capture case)")
     args = ap.parse_args()
-    if args.kernels_once:
+    if args.reference_triton:
+        reference_triton(args)
+    elif args.kernels_once:
         kernels_once(args)
     elif args.impl == "reference":
         run_reference(args)

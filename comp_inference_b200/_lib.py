@@ -87,6 +87,13 @@ SIGNATURES = {
                                             _V, _V, _S]),
     "ci_encode_legacy_segments_sizes": (C.c_int, [_V, C.c_uint32, C.c_uint32, C.c_uint32, _V, _V, _V, _V, _S]),
     "ci_encode_legacy_segments_write": (C.c_int, [_V, C.c_uint32, C.c_uint32, C.c_uint32, _V, _V, _V, C.c_uint64, _S]),
+    "ci_add_rmsnorm": (C.c_int, [_V, C.c_int64, _V, C.c_int64, _V, C.c_float, C.c_uint32, C.c_uint32, _V, C.c_int64, _V,
+                                 C.c_int64, _S]),
+    "ci_rope_kv": (C.c_int, [_V, C.c_int64, _V, C.c_int64, _V, C.c_int64, _V, _V, _V, C.c_uint32, C.c_uint32, C.c_uint32,
+                             C.c_uint32, C.c_uint32, _V, _V, _V, _S]),
+    "ci_decode_attention": (C.c_int, [_V, _V, _V, _V, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                      C.c_float, _V, C.c_int64, _S]),
+    "ci_silu_mul": (C.c_int, [_V, C.c_int64, _V, C.c_int64, C.c_uint32, C.c_uint32, _V, C.c_int64, _S]),
     "ci_allreduce_buffer_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
     "ci_allreduce_counter_bytes": (C.c_size_t, []),
     "ci_linear_allreduce_counter_bytes": (C.c_size_t, []),

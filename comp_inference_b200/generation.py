@@ -21,7 +21,12 @@ import torch.nn.functional as F
 
 
 class LlamaGreedyRunner:
-    def __init__(self, model, max_batch: int, max_len: int):
+    """``fused_glue`` (default: on a CUDA device): the decode step runs residual add + RMSNorm, rotary
+    embedding + cache write, single-query attention and SiLU * up as one kernel each (ops.add_rmsnorm, rope_kv,
+    decode_attention, silu_mul) instead of some thirty element-wise PyTorch launches per layer; the prompt pass
+    keeps the PyTorch operators."""
+
+    def __init__(self, model, max_batch: int, max_len: int, fused_glue=None):
         cfg = model.config
         self.model, self.cfg = model, cfg
         self.layers = list(model.model.layers)
@@ -49,6 +54,7 @@ class LlamaGreedyRunner:
         self.logits = None
         self._graph = None
         self._graph_batch = None
+        self.fused_glue = (self.device.type == "cuda") if fused_glue is None else bool(fused_glue)
 
     # ------------------------------------------------------------------ pieces
     @staticmethod
@@ -103,8 +109,36 @@ class LlamaGreedyRunner:
         return logits if all_logits else last
 
     # ------------------------------------------------------------------ one token
+    def _decode_step_fused(self, B):
+        """The decode step with one kernel per weightless stage (see the class docstring)."""
+        from . import ops
+        pos, m, hd = self.pos, self.model.model, self.head_dim
+        h = m.embed_tokens(self.tok[:B].view(B, 1)).view(B, -1)
+        delta = None
+        for i, layer in enumerate(self.layers):
+            ln = layer.input_layernorm
+            x, h = ops.add_rmsnorm(h if delta is None else delta, None if delta is None else h, ln.weight,
+                                   ln.variance_epsilon)
+            a = layer.self_attn
+            q, k, v = a.q_proj(x), a.k_proj(x), a.v_proj(x)
+            q = ops.rope_kv(q, k, v, self.cos, self.sin, pos, self.k_cache[i, :B], self.v_cache[i, :B], hd)
+            o = ops.decode_attention(q, self.k_cache[i, :B], self.v_cache[i, :B], pos)
+            delta = a.o_proj(o)
+            ln = layer.post_attention_layernorm
+            x, h = ops.add_rmsnorm(delta, h, ln.weight, ln.variance_epsilon)
+            mlp = layer.mlp
+            delta = mlp.down_proj(ops.silu_mul(mlp.gate_proj(x), mlp.up_proj(x)))
+        x, h = ops.add_rmsnorm(delta, h, m.norm.weight, m.norm.variance_epsilon)
+        self.logits = self.model.lm_head(x)
+        self.tok[:B] = self.logits.argmax(-1)
+        self.pos.add_(1)
+        self.steps_done.add_(1)
+        self.out[:B].index_copy_(1, self.steps_done, self.tok[:B].view(B, 1))
+
     def _decode_step(self, B):
         """Consumes self.tok (the token at position self.pos), produces the next one.  All shapes static."""
+        if self.fused_glue:
+            return self._decode_step_fused(B)
         pos = self.pos
         cos, sin = self.cos.index_select(0, pos)[None, None], self.sin.index_select(0, pos)[None, None]
         mask = (torch.arange(self.T, device=self.device) <= pos)[None, None, None, :]

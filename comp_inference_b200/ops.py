@@ -219,3 +219,66 @@ def triton_matmul(a, b):
     """Dense bf16 matmul on an already decompressed [K,N] weight (comp_inference/triton_gemm.py:324-337).
     A plain library GEMM: nothing compressed is involved, so this is torch.matmul."""
     return torch.matmul(a, b)
+
+
+# ---- the weightless steps between the linears of a decode step (csrc/glue.cu) -----------------------
+
+def _rows(t):
+    """A bf16 CUDA tensor as [rows, cols] with unit inner stride (a view where possible)."""
+    if t.dtype != torch.bfloat16:
+        raise RuntimeError(f"expected bfloat16, got {t.dtype}")
+    t2 = _lib.require_cuda(t, "tensor").reshape(-1, t.shape[-1])
+    return t2 if t2.stride(1) == 1 else t2.contiguous()
+
+
+def add_rmsnorm(x, residual, weight, eps):
+    """h = x (+ residual); returns (rmsnorm(h) * weight, h), both bf16 [..., H], in one kernel
+    (h is x itself when there is no residual)."""
+    x2 = _rows(x)
+    rows, cols = x2.shape
+    y = torch.empty((rows, cols), device=x.device, dtype=torch.bfloat16)
+    r2 = _rows(residual) if residual is not None else None
+    h = torch.empty((rows, cols), device=x.device, dtype=torch.bfloat16) if r2 is not None else None
+    _lib.check(_lib.load().ci_add_rmsnorm(_lib.ptr(x2), x2.stride(0), _lib.ptr(r2), r2.stride(0) if r2 is not None else 0,
+                                          _lib.ptr(weight), float(eps), rows, cols, _lib.ptr(y), cols, _lib.ptr(h), cols,
+                                          _lib.stream()))
+    shape = x.shape
+    return y.view(shape), (h.view(shape) if h is not None else x)
+
+
+def rope_kv(q, k, v, cos, sin, pos, k_cache, v_cache, head_dim):
+    """Rotary embedding of position ``pos`` (a one-element int64 CUDA tensor) on q [B, n_q * d] and k [B, n_kv * d],
+    and the write of k, v into the caches [B, n_kv, T, d] at that position; returns the rotated q [B, n_q, d]."""
+    q2, k2, v2 = _rows(q), _rows(k), _rows(v)
+    B = q2.shape[0]
+    n_q, n_kv = q2.shape[1] // head_dim, k2.shape[1] // head_dim
+    T = k_cache.shape[2]
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[0] >= B and k_cache.shape[1] == n_kv):
+        raise RuntimeError("KV caches must be contiguous [B, n_kv, T, d] tensors")
+    q_out = torch.empty((B, n_q, head_dim), device=q.device, dtype=torch.bfloat16)
+    _lib.check(_lib.load().ci_rope_kv(_lib.ptr(q2), q2.stride(0), _lib.ptr(k2), k2.stride(0), _lib.ptr(v2), v2.stride(0),
+                                      _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), B, n_q, n_kv, head_dim, T,
+                                      _lib.ptr(q_out), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.stream()))
+    return q_out
+
+
+def decode_attention(q, k_cache, v_cache, pos, scale=None):
+    """softmax(scale * q . K^T) . V for one query per (batch row, head) over cache positions 0 .. pos;
+    q [B, n_q, d], caches [B, n_kv, T, d]; returns [B, n_q * d]."""
+    B, n_q, d = q.shape
+    n_kv, T = k_cache.shape[1], k_cache.shape[2]
+    out = torch.empty((B, n_q * d), device=q.device, dtype=torch.bfloat16)
+    _lib.check(_lib.load().ci_decode_attention(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(pos), B, n_q,
+                                               n_kv, d, T, float(scale if scale is not None else d ** -0.5),
+                                               _lib.ptr(out), n_q * d, _lib.stream()))
+    return out
+
+
+def silu_mul(gate, up):
+    """silu(gate) * up, element-wise, bf16 [..., F]; the inputs may be column slices of a wider tensor."""
+    g2, u2 = _rows(gate), _rows(up)
+    rows, cols = g2.shape
+    out = torch.empty((rows, cols), device=gate.device, dtype=torch.bfloat16)
+    _lib.check(_lib.load().ci_silu_mul(_lib.ptr(g2), g2.stride(0), _lib.ptr(u2), u2.stride(0), rows, cols, _lib.ptr(out),
+                                       cols, _lib.stream()))
+    return out.view(*gate.shape)

@@ -311,6 +311,33 @@ int ci_encode_legacy_segments_write(const uint8_t *d_data, uint32_t rows, uint32
                                     const uint16_t *freqs, const uint16_t *cdf, uint8_t *d_stream, uint64_t stream_len,
                                     ci_stream_t stream);
 
+/* ---- between the linears of a decode step ----------------------------------------- */
+
+/* The weightless steps of a Llama-style decode step, one launch each instead of the thirty-odd element-wise
+ * launches of eager PyTorch; bf16 bits in and out, fp32 arithmetic.  No counterpart in the reference, which has
+ * no decode loop of its own (tests/test_rans_pytorch_runtime.py:89-118 calls Hugging Face's generate).
+ *
+ * ci_add_rmsnorm: h = x (+ res, if given); res_out = h (if given); y = rmsnorm(h) * weight, row by row,
+ *   with LlamaRMSNorm's rounding points.  cols <= 12288.
+ * ci_rope_kv: rotary embedding (rotate-half convention) of position *d_pos on q [batch, n_q * d] and
+ *   k [batch, n_kv * d] (row strides ldq / ldk / ldv), from bf16 cos / sin tables [T, d]; writes
+ *   q_out [batch, n_q, d], k_cache[b][h][*d_pos][:] and v_cache[b][h][*d_pos][:] (caches [batch, n_kv, T, d]).
+ * ci_decode_attention: out[b][h*d ...] = softmax(scale * q[b][h] . K[b][h / (n_q / n_kv)][0 .. *d_pos]^T) . V
+ *   (d a multiple of 64, at most 256; T <= 8192).
+ * ci_silu_mul: out = silu(gate) * up over [rows, cols] with row strides. */
+int ci_add_rmsnorm(const uint16_t *d_x, int64_t ldx, const uint16_t *d_res, int64_t ldr, const uint16_t *d_weight, float eps,
+                   uint32_t rows, uint32_t cols, uint16_t *d_y, int64_t ldy, uint16_t *d_res_out, int64_t ldo,
+                   ci_stream_t stream);
+int ci_rope_kv(const uint16_t *d_q, int64_t ldq, const uint16_t *d_k, int64_t ldk, const uint16_t *d_v, int64_t ldv,
+               const uint16_t *d_cos, const uint16_t *d_sin, const int64_t *d_pos, uint32_t batch, uint32_t n_q,
+               uint32_t n_kv, uint32_t head_dim, uint32_t T, uint16_t *d_q_out, uint16_t *d_k_cache, uint16_t *d_v_cache,
+               ci_stream_t stream);
+int ci_decode_attention(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache, const int64_t *d_pos,
+                        uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t T, float scale,
+                        uint16_t *d_out, int64_t ldo, ci_stream_t stream);
+int ci_silu_mul(const uint16_t *d_gate, int64_t ldg, const uint16_t *d_up, int64_t ldu, uint32_t rows, uint32_t cols,
+                uint16_t *d_out, int64_t ldo, ci_stream_t stream);
+
 /* ---- tensor-parallel exchange ---------------------------------------------- */
 
 /* One-shot all-reduce (sum) of a small bf16 tensor over peer memory, for the outputs of row-parallel linears.
