@@ -515,59 +515,51 @@ def full_model(rank, world, device, barrier):
 
 
 def reference_triton(args):
-    """The reference's own GPU path on this GPU, for the column next to ours: its Python package as installed
-    under baseline/_ref (``pip install --target``; git-ignored, so present only where that install was made),
-    its CUDA encoder and its Triton fused linear (comp_inference/linear_triton.py:229-314) through its public
-    functions, on the block's seven weights at batch 1.  Runs in a process of its own and prints one JSON
-    line; the caller treats any failure as "unavailable"."""
+    """The reference's own GPU kernel on this GPU, for the column next to ours: its Python package as installed
+    under baseline/_ref (``pip install --target``; git-ignored, so present only where that install was made) and
+    its Triton fused linear (comp_inference/linear_triton.py:229-314) through its public function, on the block's
+    seven weights at batch 1.  The compressed arrays it reads are produced by this repository's encoder, whose
+    bytes are identical to the reference encoder's (tests/test_gpu_parity.py::
+    test_reference_encoder_produces_the_same_bytes); the reference's own compress call is not used here because
+    its extension crashed (SIGSEGV on the host, inside RansManager.compress_tiled called from
+    rans_compress_module_weight_bf16) on the first 4096x4096 weight at its default 1024x32 tile on this box.
+    Runs in a process of its own and prints one JSON line; the caller treats any failure as "unavailable"."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref_dir, "comp_inference")):
+    if not os.path.isfile(os.path.join(ref_dir, "comp_inference", "linear_triton.py")):
         print(json.dumps({"unavailable": "the reference package is not installed under baseline/_ref"}))
         return
-    sys.path.insert(0, ref_dir)
-    import contextlib
-    import io
+    import importlib.util
+    import comp_inference_b200 as ci
     torch.cuda.set_device(0)
-    with contextlib.redirect_stdout(io.StringIO()):
-        import comp_inference as ref                            # the reference prints on import and on every call
-    out = {"package": "reference installed from its sources (pip --target baseline/_ref), stock code path"}
-    x_cache = {}
+    # the op's module by file path: it imports only torch and triton (the package __init__ would load the extension)
+    spec = importlib.util.spec_from_file_location("ref_linear_triton", os.path.join(ref_dir, "comp_inference", "linear_triton.py"))
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    out = {"kernel": "reference fused_rans_linear_triton (Triton JIT on this GPU) from baseline/_ref, stock code, "
+                     "arrays from this repository's encoder (byte-identical to the reference encoder's)"}
+    x = {K: torch.randn(1, K, generator=torch.Generator().manual_seed(2001)).to(torch.bfloat16).cuda() for K in (HIDDEN, FFN)}
 
     def run(tile_h, split_k):
         mods = {}
-        fd = os.dup(1)
-        devnull = os.open(os.devnull, os.O_WRONLY)
-        os.dup2(devnull, 1)                                     # the extension prints from C++
-        try:
-            for name, (K, N, seed) in WEIGHTS.items():
-                lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
-                lin.weight = torch.nn.Parameter(make_weight_kn(K, N, seed).t().contiguous(), requires_grad=False)
-                ref.rans_compress_module_weight(lin, tile_height=tile_h, tile_width=TILE_W, transpose_weight=True)
-                mods[name] = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in vars(lin).items()
-                              if k.startswith("exponent_") or k in ("mantissa_raw", "input_shape")}
-        finally:
-            os.dup2(fd, 1)
-            os.close(devnull)
-            os.close(fd)
+        for name, (K, N, seed) in WEIGHTS.items():
+            mods[name] = ci.compress_weight_cuda(make_weight_kn(K, N, seed).cuda(), tile_h, TILE_W)
 
-        def call(m, x):
+        def call(c, xx):
             return ref.fused_rans_linear_triton(
-                x, m["exponent_compressed_weight"], m["exponent_states"], m["exponent_tables"], m["exponent_slot_map"],
-                tuple(m["input_shape"]), m["exponent_tile_offsets"], m["exponent_tile_max_lens"],
-                m["exponent_tile_height"], m["exponent_tile_width"], m["mantissa_raw"], SPLIT_K=split_k)
+                xx, c["rans_exp_stream"], c["rans_exp_states"].view(torch.int32), c["rans_exp_tables"].view(torch.int32),
+                c["rans_exp_slot_map"], c["shape"], c["rans_exp_tile_offsets"].view(torch.int32),
+                c["rans_exp_tile_max_lens"].view(torch.int32), c["tile_height"], c["tile_width"], c["rans_man_raw"],
+                SPLIT_K=split_k)
 
         def step():
             for name, (K, N, seed) in WEIGHTS.items():
-                if K not in x_cache:
-                    x_cache[K] = torch.randn(1, K, generator=torch.Generator().manual_seed(2001)).to(torch.bfloat16).cuda()
-                call(mods[name], x_cache[K])
+                call(mods[name], x[K])
 
         step()                                                  # Triton compiles here
         torch.cuda.synchronize()
-        # parity of the reference's own kernel against a dense matmul, for the record
         K, N, seed = WEIGHTS["q_proj"]
-        y = call(mods["q_proj"], x_cache[K]).float()
-        want = x_cache[K].float() @ make_weight_kn(K, N, seed).cuda().float()
+        y = call(mods["q_proj"], x[K]).float()
+        want = x[K].float() @ make_weight_kn(K, N, seed).cuda().float()
         ms = timed(step, 20, warm=3)
         return {"ms_per_block_7_launches": ms, "tok_s": 1.0 / (ms * 1e-3),
                 "q_proj_rel_err": float((y - want).abs().max() / want.abs().max())}
@@ -577,19 +569,19 @@ def reference_triton(args):
         try:
             out[label] = run(th, sk)
         except Exception as e:
-            out[label] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            out[label] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
     print(json.dumps(out))
 
 
 def reference_triton_subprocess():
     """Runs reference_triton() in a child process (its Triton JIT and its prints stay out of this one)."""
     try:
-        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--reference-triton"], capture_output=True,
-                           text=True, timeout=600)
+        r = subprocess.run([sys.executable, "-X", "faulthandler", os.path.abspath(__file__), "--reference-triton"],
+                           capture_output=True, text=True, timeout=600)
         for line in reversed(r.stdout.strip().splitlines()):
             if line.startswith("{"):
                 return json.loads(line)
-        return {"unavailable": f"no result (exit code {r.returncode}): {r.stderr.strip()[-300:]}"}
+        return {"unavailable": f"no result (exit code {r.returncode}): {r.stderr.strip()[-1500:]}"}
     except Exception as e:
         return {"unavailable": f"{type(e).__name__}: {e}"}
 

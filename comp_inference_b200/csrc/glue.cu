@@ -36,7 +36,7 @@ __device__ __forceinline__ float block_max(float v, float *s_red) {
 
 // h = x (+ res);  res_out = h (bf16);  y = bf16(bf16(h * rsqrt(mean(h^2) + eps)) * w)   -- the rounding
 // points of LlamaRMSNorm (normalised value to bf16, then the weight product to bf16).
-__global__ void __launch_bounds__(256) k_add_rmsnorm(const uint16_t *__restrict__ x, int64_t ldx,
+__global__ void __launch_bounds__(1024) k_add_rmsnorm(const uint16_t *__restrict__ x, int64_t ldx,
                                                      const uint16_t *__restrict__ res, int64_t ldr,
                                                      const uint16_t *__restrict__ w, float eps, uint32_t cols,
                                                      uint16_t *__restrict__ y, int64_t ldy, uint16_t *__restrict__ res_out,
@@ -98,17 +98,21 @@ __global__ void k_rope_kv(const uint16_t *__restrict__ q, int64_t ldq, const uin
 }
 
 // One query per (batch row, head) against cache positions 0 .. pos: softmax(q . K^T / sqrt(d)) . V.
-// grid = (heads_q, batch), block = 128 threads; head dimension d <= 256, a multiple of 64.
-__global__ void __launch_bounds__(128) k_decode_attention(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_cache,
-                                                          const uint16_t *__restrict__ v_cache,
-                                                          const int64_t *__restrict__ pos_p, uint32_t n_q, uint32_t n_kv,
-                                                          uint32_t d, uint32_t T, float scale, uint16_t *__restrict__ out,
-                                                          int64_t ldo) {
-    extern __shared__ float s_mem[];                            // [T] scores, then [d] query
+// grid = (heads_q, batch), block = 512 threads; head dimension d <= 256, a multiple of 64.
+// The cache rows come from L2 / HBM, so what matters is how many loads are in flight: the score pass keeps
+// four positions (eight 4-byte loads) per lane in the air, the value pass eight positions per thread.
+constexpr uint32_t kAttnThreads = 512;
+
+__global__ void __launch_bounds__(kAttnThreads) k_decode_attention(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k_cache,
+                                                                   const uint16_t *__restrict__ v_cache,
+                                                                   const int64_t *__restrict__ pos_p, uint32_t n_q,
+                                                                   uint32_t n_kv, uint32_t d, uint32_t T, float scale,
+                                                                   uint16_t *__restrict__ out, int64_t ldo) {
+    extern __shared__ float s_mem[];                            // [T] scores, [d] query, [groups][d] partial outputs
     __shared__ float s_red[32];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    float *s_score = s_mem, *s_q = s_mem + T;
+    float *s_score = s_mem, *s_q = s_mem + T, *s_part = s_q + d;
     const uint32_t h = blockIdx.x, b = blockIdx.y, kvh = h / (n_q / n_kv);
     int64_t pos = *pos_p;
     if (pos < 0) pos = 0;
@@ -121,16 +125,30 @@ __global__ void __launch_bounds__(128) k_decode_attention(const uint16_t *__rest
     __syncthreads();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     float mx = -INFINITY;
-    for (uint32_t t = warp; t < n_pos; t += nw) {               // a warp per position, lanes across the head dimension
-        const uint16_t *kr = kb + (size_t)t * d;
-        float acc = 0.f;
+    // scores: a warp takes four positions per round (t, t + nw, t + 2 nw, t + 3 nw), lanes across the head dimension
+    for (uint32_t t0 = warp; t0 < n_pos; t0 += 4 * nw) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (uint32_t i = lane * 2; i < d; i += 64) {
-            const uint32_t two = *reinterpret_cast<const uint32_t *>(kr + i);
-            acc += s_q[i] * __uint_as_float(two << 16) + s_q[i + 1] * __uint_as_float(two & 0xFFFF0000u);
+            uint32_t two[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t t = min(t0 + u * nw, n_pos - 1);      // clamped: the result of a repeated row is dropped below
+                two[u] = __ldg(reinterpret_cast<const uint32_t *>(kb + (size_t)t * d + i));
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                acc[u] += s_q[i] * __uint_as_float(two[u] << 16) + s_q[i + 1] * __uint_as_float(two[u] & 0xFFFF0000u);
         }
-        for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
-        if (lane == 0) s_score[t] = acc;
-        mx = fmaxf(mx, acc);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float a = acc[u];
+            for (int o = 16; o >= 1; o >>= 1) a += __shfl_xor_sync(kFull, a, o);
+            const uint32_t t = t0 + u * nw;
+            if (t < n_pos) {
+                if (lane == 0) s_score[t] = a;
+                mx = fmaxf(mx, a);
+            }
+        }
     }
     mx = block_max(mx, s_red);
     float sum = 0.f;
@@ -141,17 +159,36 @@ __global__ void __launch_bounds__(128) k_decode_attention(const uint16_t *__rest
     }
     sum = block_sum(sum, s_red);                                // (its barriers also publish s_score)
     const float inv = 1.f / sum;
-    for (uint32_t i = threadIdx.x * 2; i < d; i += blockDim.x * 2) {   // a thread per pair of output dimensions
-        float a0 = 0.f, a1 = 0.f;
-        for (uint32_t t = 0; t < n_pos; ++t) {
-            const uint32_t two = *reinterpret_cast<const uint32_t *>(vb + (size_t)t * d + i);
-            const float p = s_score[t];
-            a0 += p * __uint_as_float(two << 16);
-            a1 += p * __uint_as_float(two & 0xFFFF0000u);
+    // values: d / 2 threads form a group (a thread per pair of output dimensions), group g takes positions
+    // g, g + groups, ...; eight positions per round
+    const uint32_t per_group = d / 2, groups = blockDim.x / per_group;
+    const uint32_t grp = threadIdx.x / per_group, i = (threadIdx.x % per_group) * 2;
+    float a0 = 0.f, a1 = 0.f;
+    if (grp < groups) {
+        for (uint32_t t0 = grp; t0 < n_pos; t0 += 8 * groups) {
+            uint32_t two[8];
+            float p[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t t = t0 + u * groups;
+                const bool in = t < n_pos;
+                two[u] = __ldg(reinterpret_cast<const uint32_t *>(vb + (size_t)(in ? t : t0) * d + i));
+                p[u] = in ? s_score[t] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                a0 += p[u] * __uint_as_float(two[u] << 16);
+                a1 += p[u] * __uint_as_float(two[u] & 0xFFFF0000u);
+            }
         }
-        uint16_t *o = out + (size_t)b * ldo + (size_t)h * d + i;
-        o[0] = float_to_bf16_bits(a0 * inv);
-        o[1] = float_to_bf16_bits(a1 * inv);
+        s_part[grp * d + i] = a0;
+        s_part[grp * d + i + 1] = a1;
+    }
+    __syncthreads();
+    for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) {
+        float v = 0.f;
+        for (uint32_t gI = 0; gI < groups; ++gI) v += s_part[gI * d + c];
+        out[(size_t)b * ldo + (size_t)h * d + c] = float_to_bf16_bits(v * inv);
     }
 }
 
@@ -199,7 +236,9 @@ int ci_add_rmsnorm(const uint16_t *d_x, int64_t ldx, const uint16_t *d_res, int6
     CI_REQUIRE(d_x && d_weight && d_y, "null pointer");
     CI_REQUIRE(cols > 0 && cols <= 12288, "row length %u outside (0, 12288]", cols);
     if (rows == 0) return CI_OK;
-    return launch_pdl(k_add_rmsnorm, dim3(rows), dim3(256), (size_t)cols * sizeof(float), (cudaStream_t)stream, d_x, ldx,
+    // few rows (decode steps): the row is short and latency-bound, so spread it over many threads
+    const uint32_t threads = cols >= 4096 ? 1024u : (cols >= 1024 ? 512u : 256u);
+    return launch_pdl(k_add_rmsnorm, dim3(rows), dim3(threads), (size_t)cols * sizeof(float), (cudaStream_t)stream, d_x, ldx,
                       d_res, ldr, d_weight, eps, cols, d_y, ldy, d_res_out, ldo);
 }
 
@@ -223,8 +262,9 @@ int ci_decode_attention(const uint16_t *d_q, const uint16_t *d_k_cache, const ui
     CI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "%u query heads over %u key/value heads", n_q, n_kv);
     CI_REQUIRE(T > 0 && T <= 8192, "cache length %u outside (0, 8192]", T);
     if (batch == 0) return CI_OK;
-    return launch_pdl(k_decode_attention, dim3(n_q, batch), dim3(128), (size_t)(T + head_dim) * sizeof(float),
-                      (cudaStream_t)stream, d_q, d_k_cache, d_v_cache, d_pos, n_q, n_kv, head_dim, T, scale, d_out, ldo);
+    const uint32_t groups = kAttnThreads / (head_dim / 2);
+    return launch_pdl(k_decode_attention, dim3(n_q, batch), dim3(kAttnThreads),
+                      (size_t)(T + head_dim + groups * head_dim) * sizeof(float), (cudaStream_t)stream, d_q, d_k_cache, d_v_cache, d_pos, n_q, n_kv, head_dim, T, scale, d_out, ldo);
 }
 
 int ci_silu_mul(const uint16_t *d_gate, int64_t ldg, const uint16_t *d_up, int64_t ldu, uint32_t rows, uint32_t cols,
