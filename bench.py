@@ -832,16 +832,8 @@ def run_ours(args):
     torch.cuda.empty_cache()
     if reducer is not None:
         reducer.close()
-    if not args.no_full_model:
-        try:
-            extra["full_model"] = full_model(rank, world, device, barrier if world > 1 else None)
-        except Exception as e:                                  # the headline line must still be printed
-            extra["full_model"] = {"error": f"{type(e).__name__}: {e}"}
-            if world > 1:
-                raise
-        trace("full model done")
-
     failed = tp_err is not None and tp_err > 1e-2
+    line = None
     if rank == 0:
         # algorithmic bytes of one step on one GPU: compressed weights + activations in + results out
         act = sum(2 * M * (WEIGHTS[members[0]][0] + sum(WEIGHTS[n][1] for n in members)) for _, members, _ in LAYERS)
@@ -870,27 +862,59 @@ def run_ours(args):
                 "clocks": clocks, "notes": notes}
         if tp_err is not None:
             extra["tp_parity_rel_err"] = tp_err
-        if extra:
-            line["extra"] = extra
-        if world == 1 and not args.no_cpu:
-            val, ms, cores = cpu_baseline_run(M, 1, 1)
-            line["cpu_baseline"] = {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
-                                    "sample": "1 full step after 1 warm-up step (the block's weights decoded and "
-                                              "multiplied), CPU restatement of the reference algorithm, all host cores"}
-        print(json.dumps(line))
-        if failed:
-            print(f"tensor-parallel result differs from the unsharded block by {tp_err:.3e} (> 1e-2)", file=sys.stderr)
+        line["extra"] = extra
+
+    def finish(code):
+        """Prints the line (rank 0) and leaves.  Multi-rank runs leave through os._exit: communicator clean-up is
+        left to process exit (tearing the process group down after graphs that referred to it blocked for
+        minutes on a 2-GPU box); all graphs and peer buffers are gone by then."""
+        if rank == 0:
+            if not line["extra"]:
+                del line["extra"]
+            print(json.dumps(line))
+            if failed:
+                print(f"tensor-parallel result differs from the unsharded block by {tp_err:.3e} (> 1e-2)", file=sys.stderr)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        if world > 1:
+            os._exit(code)
+        if code:
+            sys.exit(code)
+
+    if not args.no_full_model:
+        # The block's figures above are complete.  The whole-model run must not be able to lose them: if it raises
+        # on some rank, or does not come back (a rank that failed leaves its peers inside a collective), every
+        # rank gives up after a deadline, rank 0 prints the line with the reason, and the processes leave.
+        def give_up():
+            if rank == 0:
+                extra["full_model"] = {"error": f"did not finish within {args.full_model_deadline} s"}
+            finish(1 if failed else 0)
+            os._exit(1 if failed else 0)
+
+        watchdog = threading.Timer(args.full_model_deadline + (0 if rank == 0 else 10), give_up)
+        watchdog.daemon = True
+        watchdog.start()
+        try:
+            extra["full_model"] = full_model(rank, world, device, barrier if world > 1 else None)
+            trace("full model done")
+        except Exception as e:
+            extra["full_model"] = {"error": f"{type(e).__name__}: {str(e)[:500]}"}
+            trace(f"full model failed: {e}")
+            if world > 1:                                       # the peers may be waiting for this rank: no more collectives
+                watchdog.cancel()
+                finish(1 if failed else 0)
+        watchdog.cancel()
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        val, ms, cores = cpu_baseline_run(M, 1, 1)
+        line["cpu_baseline"] = {"value": val, "unit": "tok/s", "cores": cores, "kind": "port",
+                                "sample": "1 full step after 1 warm-up step (the block's weights decoded and "
+                                          "multiplied), CPU restatement of the reference algorithm, all host cores"}
     if world > 1:
-        # Communicator clean-up is left to process exit: tearing the process group down after graphs that
-        # referred to it blocked for minutes on a 2-GPU box.  All graphs and peer buffers are gone by now.
         trace("shutting down")
         torch.cuda.synchronize()
         dist.barrier()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(1 if failed else 0)
-    if failed:
-        sys.exit(1)
+    finish(1 if failed else 0)
 
 
 def main():
@@ -903,6 +927,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary metrics (N = 1)")
     ap.add_argument("--no-full-model", action="store_true", help="skip the whole-model run")
+    ap.add_argument("--full-model-deadline", type=int, default=420,
+                    help="seconds after which a whole-model run that has not come back is abandoned (the line is still printed)")
     ap.add_argument("--no-fuse-exchange", action="store_true",
                     help="N > 1: all-reduce with the one-shot kernel behind the row-parallel GEMV instead of inside it")
     ap.add_argument("--reference-triton", action="store_true",

@@ -34,6 +34,8 @@ struct MmaArgs {
     uint32_t per_warp;     // units per warp
     uint32_t total;        // units in the matrix
     uint32_t x_aligned;    // activations can be read as 32-bit pairs
+    uint32_t red_off;      // shared-memory reduction area (offset from the window base): [red_slots] tickets, then
+    uint32_t red_slots;    //   [red_slots][2][32] fp32 partials; 0 = none (more than two activation rows)
     uint32_t *status;      // set non-zero if a wait ran out
 };
 
@@ -137,6 +139,13 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
     uint32_t nx_begin = __shfl_sync(kFull, d_begin, 0), nx_end = __shfl_sync(kFull, d_end, 0);
     if (lo < hi) issue(lo, 0, nx_begin, nx_end);
     load_lut(s_lut, a.lut, a.tables, a.slot_map);
+    // Column groups whose units all sit in this CTA are reduced through shared memory (tickets zeroed here)
+    // instead of the workspace in global memory: no L2 round trip between the last decode step and the output.
+    uint32_t *s_ticket = reinterpret_cast<uint32_t *>(smem + p.red_off);
+    float *s_part = reinterpret_cast<float *>(smem + p.red_off) + p.red_slots;
+    for (uint32_t i = threadIdx.x; i < p.red_slots; i += blockDim.x) s_ticket[i] = 0;
+    const uint32_t cta_w0 = blockIdx.x * W;                     // grid rank of this CTA's first warp
+    const uint32_t cta_g0 = (cta_w0 * p.per_warp) / g.tiles_k;  // first column group this CTA touches
     __syncthreads();
     // Only the weight was read so far.  Under programmatic dependent launch the activations, the workspace
     // and the output may still belong to the previous kernel of the stream: wait for it, then let the next
@@ -193,22 +202,39 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
             }
             return;
         }
-        // Slot gw + grp is unique: along the unit order both the warp rank and the group only grow.
-        float *mine = a.partial + (size_t)(gw + grp) * a.M * 32;
-#pragma unroll
-        for (int nb = 0; nb < 4; ++nb) {
-            if (r0 < a.M) *reinterpret_cast<float2 *>(mine + r0 * 32 + nb * 8 + c0) = make_float2(acc[nb][0], acc[nb][1]);
-            if (r0 + 8 < a.M)
-                *reinterpret_cast<float2 *>(mine + (r0 + 8) * 32 + nb * 8 + c0) = make_float2(acc[nb][2], acc[nb][3]);
-        }
-        // One acquire-release ticket: the warp barrier orders the lanes' partial stores before lane 0's
-        // release, and the last arriver's acquire before the lanes' loads.
-        __syncwarp();
+        // All warps of this group in this CTA (and at most two activation rows): shared-memory slots and ticket.
+        const bool local = p.red_slots != 0 && first_w >= cta_w0 && last_w < cta_w0 + W;
         uint32_t last = 0;
-        if (lane == 0) {
-            uint32_t seen;
-            asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.tickets + grp) : "memory");
-            last = seen == count - 1;
+        if (local) {
+            // Slot (warp + group), both relative to this CTA: unique for the same reason as below.
+            float *mine = s_part + (size_t)(warp + grp - cta_g0) * 64;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb)
+                if (r0 < a.M) *reinterpret_cast<float2 *>(mine + r0 * 32 + nb * 8 + c0) = make_float2(acc[nb][0], acc[nb][1]);
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t seen;
+                asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;"
+                             : "=r"(seen) : "r"(smem_u32(s_ticket + (grp - cta_g0))) : "memory");
+                last = seen == count - 1;
+            }
+        } else {
+            // Slot gw + grp is unique: along the unit order both the warp rank and the group only grow.
+            float *mine = a.partial + (size_t)(gw + grp) * a.M * 32;
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) {
+                if (r0 < a.M) *reinterpret_cast<float2 *>(mine + r0 * 32 + nb * 8 + c0) = make_float2(acc[nb][0], acc[nb][1]);
+                if (r0 + 8 < a.M)
+                    *reinterpret_cast<float2 *>(mine + (r0 + 8) * 32 + nb * 8 + c0) = make_float2(acc[nb][2], acc[nb][3]);
+            }
+            // One acquire-release ticket: the warp barrier orders the lanes' partial stores before lane 0's
+            // release, and the last arriver's acquire before the lanes' loads.
+            __syncwarp();
+            if (lane == 0) {
+                uint32_t seen;
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(seen) : "l"(a.tickets + grp) : "memory");
+                last = seen == count - 1;
+            }
         }
         last = __shfl_sync(kFull, last, 0);
         __syncwarp();                                           // lane 0's acquire is ordered before every lane's loads
@@ -216,9 +242,16 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
         if (a.M <= 2) {
             // One or two activation rows: lane = column, up to sixteen partials of both rows in flight at
             // once, so the whole reduction of a 4096-row matrix costs one L2 round trip.  Same summation
-            // order as below (partial first_w, first_w + 1, ...).
+            // order everywhere (partial first_w, first_w + 1, ...), so the result does not depend on the path.
             float s0 = 0.f, s1 = 0.f;
             const bool two = a.M == 2;
+            if (local) {
+                for (uint32_t w = first_w; w <= last_w; ++w) {
+                    const float *src = s_part + (size_t)(w - cta_w0 + grp - cta_g0) * 64 + lane;
+                    s0 += src[0];
+                    if (two) s1 += src[32];
+                }
+            } else
             for (uint32_t w0 = first_w; w0 <= last_w; w0 += 16) {
                 float t0[16], t1[16];
 #pragma unroll
@@ -253,7 +286,7 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
                 if (two) a.y[(size_t)a.ldy + n] = float_to_bf16_bits(s1 + b);
             }
             __syncwarp();
-            if (lane == 0) a.tickets[grp] = 0;
+            if (lane == 0 && !local) a.tickets[grp] = 0;
             return;
         }
         // All loads of a batch of four partials are issued before any of them is used: a plain running
@@ -503,17 +536,41 @@ int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     uint32_t w_max = ((uint32_t)max_smem - fixed) / p.warp_bytes;
     if (w_max > 16) w_max = 16;
 
-    // Units per warp must be a whole number: pick the warp count whose grid wastes the least.
+    // Room for the shared-memory reduction of column groups that sit inside one CTA (one or two activation rows):
+    // at most w + w * per_warp / tiles_k + 2 slots of [2][32] floats and as many tickets.
+    const bool small_m = a.M <= 2;
+    auto red_slots_for = [&](uint32_t w, uint64_t per) { return small_m ? (uint32_t)(w + w * per / g.tiles_k + 2) : 0u; };
+    auto fits = [&](uint32_t w, uint64_t per) {
+        return fixed + (size_t)w * p.warp_bytes + (size_t)red_slots_for(w, per) * 260 + 16 <= (size_t)max_smem;
+    };
+
+    // Units per warp must be a whole number: pick the warp count whose grid wastes the least; among warp counts
+    // within 3 % of the best, prefer one whose CTAs hold whole column groups (their reduction then never leaves
+    // the multiprocessor).
     const uint32_t P = (uint32_t)sm_count();
     p.total = g.groups * g.tiles_k;
-    uint32_t best_w = w_max;
+    uint32_t best_w = 0;
     double best = -1.0;
-    for (uint32_t w = 4; w <= w_max; ++w) {
-        uint64_t slots = (uint64_t)P * w, per = (p.total + slots - 1) / slots;
+    auto eff_of = [&](uint32_t w, uint64_t &per) {
+        const uint64_t slots = (uint64_t)P * w;
+        per = (p.total + slots - 1) / slots;
         double eff = (double)p.total / (double)(slots * per);
         if (w < 8) eff *= w / 8.0;                              // too few warps cannot hide the decode chain
+        return eff;
+    };
+    for (uint32_t w = 4; w <= w_max; ++w) {
+        uint64_t per;
+        const double eff = eff_of(w, per);
+        if (!fits(w, per)) continue;
         if (eff >= best) { best = eff; best_w = w; }
     }
+    if (best_w == 0) return 1;
+    if (small_m)
+        for (uint32_t w = w_max; w >= 4; --w) {
+            uint64_t per;
+            const double eff = eff_of(w, per);
+            if (fits(w, per) && eff >= best - 0.03 && (w * per) % g.tiles_k == 0) { best_w = w; break; }
+        }
     const uint64_t slots = (uint64_t)P * best_w;
     p.per_warp = (uint32_t)((p.total + slots - 1) / slots);
     const uint32_t warps_needed = (p.total + p.per_warp - 1) / p.per_warp;
@@ -521,7 +578,9 @@ int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     p.x_aligned = ((reinterpret_cast<uintptr_t>(a.x) & 3u) == 0 && (a.ldx & 1) == 0) ? 1u : 0u;
     p.status = a.tickets + (kTicketBytes - 1);
 
-    const size_t smem = fixed + (size_t)best_w * p.warp_bytes;
+    p.red_slots = red_slots_for(best_w, p.per_warp);
+    p.red_off = (fixed + best_w * p.warp_bytes + 15u) & ~15u;
+    const size_t smem = p.red_off + (size_t)p.red_slots * 260;
     if (a.dry_run) return CI_OK;                                // qualification only
     if (g.tw == 32) return launch_tw<32>(p, blocks, best_w, smem, max_smem, s);
     if (g.tw == 16) return launch_tw<16>(p, blocks, best_w, smem, max_smem, s);
