@@ -820,8 +820,9 @@ def run_ours(args):
     if world == 1 and not args.no_extra:
         extra = secondary_metrics(mods, dense, device, peak_hbm, peak_tf, src)
         trace("secondary metrics done")
-        extra["reference_triton_b200"] = reference_triton_subprocess()
-        trace("reference Triton leg done")
+        if not args.no_reference_leg:
+            extra["reference_triton_b200"] = reference_triton_subprocess()
+            trace("reference Triton leg done")
     del dense
     # the block's graphs refer to the group's communicators; drop them before the model run sets up its own
     del graph, y_graph, e2e_graph, y_e2e
@@ -927,6 +928,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary metrics (N = 1)")
     ap.add_argument("--no-full-model", action="store_true", help="skip the whole-model run")
+    ap.add_argument("--no-reference-leg", action="store_true",
+                    help="skip the child process that times the reference's own Triton kernel")
     ap.add_argument("--full-model-deadline", type=int, default=420,
                     help="seconds after which a whole-model run that has not come back is abandoned (the line is still printed)")
     ap.add_argument("--no-fuse-exchange", action="store_true",
