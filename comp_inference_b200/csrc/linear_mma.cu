@@ -34,8 +34,8 @@ struct MmaArgs {
     uint32_t per_warp;     // units per warp
     uint32_t total;        // units in the matrix
     uint32_t x_aligned;    // activations can be read as 32-bit pairs
-    uint32_t red_off;      // shared-memory reduction area (offset from the window base): [red_slots] tickets, then
-    uint32_t red_slots;    //   [red_slots][2][32] fp32 partials; 0 = none (more than two activation rows)
+    uint32_t red_off;      // shared-memory reduction area (16-byte aligned offset from the window base):
+    uint32_t red_slots;    //   [red_slots][2][32] fp32 partials, then [red_slots] tickets; 0 = none (more than two rows)
     uint32_t *status;      // set non-zero if a wait ran out
 };
 
@@ -141,8 +141,8 @@ __global__ void __launch_bounds__(512, 1) k_linear_mma(const __grid_constant__ M
     load_lut(s_lut, a.lut, a.tables, a.slot_map);
     // Column groups whose units all sit in this CTA are reduced through shared memory (tickets zeroed here)
     // instead of the workspace in global memory: no L2 round trip between the last decode step and the output.
-    uint32_t *s_ticket = reinterpret_cast<uint32_t *>(smem + p.red_off);
-    float *s_part = reinterpret_cast<float *>(smem + p.red_off) + p.red_slots;
+    float *s_part = reinterpret_cast<float *>(smem + p.red_off);                 // 8-byte stores: keep it aligned
+    uint32_t *s_ticket = reinterpret_cast<uint32_t *>(s_part + (size_t)p.red_slots * 64);
     for (uint32_t i = threadIdx.x; i < p.red_slots; i += blockDim.x) s_ticket[i] = 0;
     const uint32_t cta_w0 = blockIdx.x * W;                     // grid rank of this CTA's first warp
     const uint32_t cta_g0 = (cta_w0 * p.per_warp) / g.tiles_k;  // first column group this CTA touches
@@ -561,16 +561,19 @@ int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     for (uint32_t w = 4; w <= w_max; ++w) {
         uint64_t per;
         const double eff = eff_of(w, per);
-        if (!fits(w, per)) continue;
         if (eff >= best) { best = eff; best_w = w; }
     }
     if (best_w == 0) return 1;
-    if (small_m)
+    bool use_red = false;                                       // the reduction area never costs a warp: it is dropped instead
+    if (small_m) {
+        uint64_t per;
+        eff_of(best_w, per);
+        use_red = fits(best_w, per);
         for (uint32_t w = w_max; w >= 4; --w) {
-            uint64_t per;
             const double eff = eff_of(w, per);
-            if (fits(w, per) && eff >= best - 0.03 && (w * per) % g.tiles_k == 0) { best_w = w; break; }
+            if (fits(w, per) && eff >= 0.97 * best && (w * per) % g.tiles_k == 0) { best_w = w; use_red = true; break; }
         }
+    }
     const uint64_t slots = (uint64_t)P * best_w;
     p.per_warp = (uint32_t)((p.total + slots - 1) / slots);
     const uint32_t warps_needed = (p.total + p.per_warp - 1) / p.per_warp;
@@ -578,7 +581,7 @@ int launch_linear_mma(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     p.x_aligned = ((reinterpret_cast<uintptr_t>(a.x) & 3u) == 0 && (a.ldx & 1) == 0) ? 1u : 0u;
     p.status = a.tickets + (kTicketBytes - 1);
 
-    p.red_slots = red_slots_for(best_w, p.per_warp);
+    p.red_slots = use_red ? red_slots_for(best_w, p.per_warp) : 0u;
     p.red_off = (fixed + best_w * p.warp_bytes + 15u) & ~15u;
     const size_t smem = p.red_off + (size_t)p.red_slots * 260;
     if (a.dry_run) return CI_OK;                                // qualification only
