@@ -221,6 +221,7 @@ def parity_table(mods, dense, device):
     elements that meet it."""
     rows = []
     for name, m in mods.items():
+        m.prefill_policy = "fused"                              # the table is about this repository's kernels
         W = dense[name].float()
         for M in (1, 4, 16, 512):
             x = torch.randn(M, m.in_features, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).to(device)
@@ -230,6 +231,7 @@ def parity_table(mods, dense, device):
             rows.append({"layer": name, "K": m.in_features, "N": m.out_features, "M": M,
                          "max_rel": float(err.max() / ref.abs().max()),
                          "allclose_1e-2": float((err <= 1e-2 + 1e-2 * ref.abs()).float().mean())})
+        m.prefill_policy = "auto"
         del W
     return rows
 
@@ -319,6 +321,8 @@ def secondary_metrics(mods, dense, device, peak_hbm, peak_tf, src):
 
     from comp_inference_b200 import _lib
     _lib.reserve_workspace(device, (1 << 16) + 8 * 2048 * 2 * FFN * 4)   # room for 8 partial sums of the widest layer
+    for m in mods.values():
+        m.prefill_policy = "fused"
     prefill = {}
     for M in (512, 2048):
         x = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).to(device)
@@ -337,7 +341,10 @@ def secondary_metrics(mods, dense, device, peak_hbm, peak_tf, src):
                                    "TFLOPs": flops_per_row * M / (ms * 1e-3) / 1e12,
                                    "kernel": "k_decode4 into a scratch buffer + cuBLAS bf16 GEMM"}
         prefill[f"M{M}"] = row
-    out["prefill"] = dict(prefill, kernel="k_linear_gemm (tcgen05.mma, TMEM accumulators)", peak_source=f"of {src} sustained bf16")
+    for m in mods.values():
+        m.prefill_policy = "auto"
+    out["prefill"] = dict(prefill, kernel="k_linear_gemm (tcgen05.mma, TMEM accumulators); 'auto' = the library's own split-K choice",
+                          peak_source=f"of {src} sustained bf16")
     out["prefill_M512"] = dict(prefill["M512"]["auto"], kernel="k_linear_gemm (tcgen05.mma, TMEM accumulators)")
     out["prefill_M512_decode_then_gemm"] = prefill["M512"]["decode_then_gemm"]
 
@@ -458,6 +465,7 @@ def full_model(rank, world, device, barrier):
            "compressed_GB": comp_bytes / 1e9, "modules": kinds,
            "parallelism": "single GPU" if world == 1 else f"tp{world}: column/row shards, vocabulary-parallel LM head",
            "decode": "one CUDA graph replay per token (embedding gather, 32 layers, LM head, argmax, KV update)",
+           "prefill": "module default: stand-alone decode + library GEMM from 256 rows up (prefill_policy='auto')",
            "parity_note": "weights are bit-identical to the dense model's; a random-init model has near-tied logits, "
                           "so free-running greedy sequences part at the first near-tie.  near_best = share of "
                           "generated tokens whose dense-bf16 logit (dense model teacher-forced on that sequence) is "
@@ -594,7 +602,7 @@ def kernels_once(args):
     K = N = HIDDEN
     W = make_weight_kn(K, N, 1001).cuda()
     c = ci.compress_weight_cuda(W, TILE_H, TILE_W)
-    m = ci.RansLinear(K, N, c["tile_height"], c["tile_width"]).load_compressed(c).cuda()
+    m = ci.RansLinear(K, N, c["tile_height"], c["tile_width"], prefill_policy="fused").load_compressed(c).cuda()
     g = torch.Generator().manual_seed(7)
     x1 = torch.randn(1, K, generator=g).to(torch.bfloat16).cuda()
     x512 = torch.randn(512, K, generator=g).to(torch.bfloat16).cuda()

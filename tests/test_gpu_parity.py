@@ -322,7 +322,7 @@ def test_prefill_policies_agree(ci):
     bias = torch.randn(N, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
     x = torch.randn(M, K, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).cuda()
     ref = (x.double().cpu() @ W.double() + bias.double().cpu()).numpy()
-    for policy in ("fused", "decode_then_gemm"):
+    for policy in ("fused", "decode_then_gemm", "auto"):
         lin = ci.RansLinear(K, N, 128, 32, has_bias=True, prefill_policy=policy).load_compressed(c).cuda()
         lin.bias = bias
         assert rel_err(lin(x).float().cpu().numpy(), ref) <= REL_TOL, policy
