@@ -542,7 +542,10 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     // That pays once the multiprocessors are saturated (about eight warps each); a small matrix -- a
     // tensor-parallel shard, say -- is latency bound and finishes sooner with the shorter units
     // (measured cross-over: 4096 x 2048 at tile height 128).
-    if (p.total < P * 6) return 1;
+#ifndef CI_MMA4_MIN_UNITS
+#define CI_MMA4_MIN_UNITS 6
+#endif
+    if (p.total < P * CI_MMA4_MIN_UNITS) return 1;
     uint32_t best_w = w_max;
     double best = -1.0;
     for (uint32_t w = 4; w <= w_max; ++w) {
