@@ -91,8 +91,9 @@ SIGNATURES = {
                                  C.c_int64, _S]),
     "ci_rope_kv": (C.c_int, [_V, C.c_int64, _V, C.c_int64, _V, C.c_int64, _V, _V, _V, C.c_uint32, C.c_uint32, C.c_uint32,
                              C.c_uint32, C.c_uint32, _V, _V, _V, _S]),
+    "ci_decode_attention_workspace_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "ci_decode_attention": (C.c_int, [_V, _V, _V, _V, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
-                                      C.c_float, _V, C.c_int64, _S]),
+                                      C.c_float, _V, C.c_size_t, _V, C.c_int64, _S]),
     "ci_silu_mul": (C.c_int, [_V, C.c_int64, _V, C.c_int64, C.c_uint32, C.c_uint32, _V, C.c_int64, _S]),
     "ci_allreduce_buffer_bytes": (C.c_size_t, [C.c_uint32, C.c_uint32]),
     "ci_allreduce_counter_bytes": (C.c_size_t, []),

@@ -268,10 +268,29 @@ def decode_attention(q, k_cache, v_cache, pos, scale=None):
     B, n_q, d = q.shape
     n_kv, T = k_cache.shape[1], k_cache.shape[2]
     out = torch.empty((B, n_q * d), device=q.device, dtype=torch.bfloat16)
-    _lib.check(_lib.load().ci_decode_attention(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(pos), B, n_q,
-                                               n_kv, d, T, float(scale if scale is not None else d ** -0.5),
-                                               _lib.ptr(out), n_q * d, _lib.stream()))
+    lib = _lib.load()
+    ws = _attention_workspace(q.device, lib.ci_decode_attention_workspace_bytes(B, n_q, d, T))
+    _lib.check(lib.ci_decode_attention(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(pos), B, n_q,
+                                       n_kv, d, T, float(scale if scale is not None else d ** -0.5),
+                                       _lib.ptr(ws), ws.numel(), _lib.ptr(out), n_q * d, _lib.stream()))
     return out
+
+
+_attn_ws = {}
+_attn_retired = []
+
+
+def _attention_workspace(device, nbytes):
+    """Zeroed scratch of the attention kernel, one per (device, stream), never freed once handed out (a captured
+    graph keeps the address)."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _attn_ws.get(key)
+    if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _attn_retired.append(ws)
+        ws = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _attn_ws[key] = ws
+    return ws
 
 
 def silu_mul(gate, up):

@@ -323,7 +323,9 @@ int ci_encode_legacy_segments_write(const uint8_t *d_data, uint32_t rows, uint32
  *   k [batch, n_kv * d] (row strides ldq / ldk / ldv), from bf16 cos / sin tables [T, d]; writes
  *   q_out [batch, n_q, d], k_cache[b][h][*d_pos][:] and v_cache[b][h][*d_pos][:] (caches [batch, n_kv, T, d]).
  * ci_decode_attention: out[b][h*d ...] = softmax(scale * q[b][h] . K[b][h / (n_q / n_kv)][0 .. *d_pos]^T) . V
- *   (d a multiple of 64, at most 256; T <= 8192).
+ *   (d = 64, 128 or 256; T <= 32768).  The positions of a query are cut into ranges, one CTA each; d_workspace
+ *   (ci_decode_attention_workspace_bytes, 16-byte aligned, zeroed once; calls leave its ticket area zeroed) holds the
+ *   ranges' partial results.  Calls that overlap on the GPU must not share a workspace.
  * ci_silu_mul: out = silu(gate) * up over [rows, cols] with row strides. */
 int ci_add_rmsnorm(const uint16_t *d_x, int64_t ldx, const uint16_t *d_res, int64_t ldr, const uint16_t *d_weight, float eps,
                    uint32_t rows, uint32_t cols, uint16_t *d_y, int64_t ldy, uint16_t *d_res_out, int64_t ldo,
@@ -332,9 +334,10 @@ int ci_rope_kv(const uint16_t *d_q, int64_t ldq, const uint16_t *d_k, int64_t ld
                const uint16_t *d_cos, const uint16_t *d_sin, const int64_t *d_pos, uint32_t batch, uint32_t n_q,
                uint32_t n_kv, uint32_t head_dim, uint32_t T, uint16_t *d_q_out, uint16_t *d_k_cache, uint16_t *d_v_cache,
                ci_stream_t stream);
+size_t ci_decode_attention_workspace_bytes(uint32_t batch, uint32_t n_q, uint32_t head_dim, uint32_t T);
 int ci_decode_attention(const uint16_t *d_q, const uint16_t *d_k_cache, const uint16_t *d_v_cache, const int64_t *d_pos,
                         uint32_t batch, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t T, float scale,
-                        uint16_t *d_out, int64_t ldo, ci_stream_t stream);
+                        void *d_workspace, size_t workspace_bytes, uint16_t *d_out, int64_t ldo, ci_stream_t stream);
 int ci_silu_mul(const uint16_t *d_gate, int64_t ldg, const uint16_t *d_up, int64_t ldu, uint32_t rows, uint32_t cols,
                 uint16_t *d_out, int64_t ldo, ci_stream_t stream);
 
