@@ -260,3 +260,63 @@ def compress_bf16(raw_u16_KN, th, tw, nthreads=None):
     r["mantissa"] = interleave_mantissa(m, r.tile_height, r.tile_width)
     r["freqs"], r["cdf"] = f, c
     return r
+
+
+# ---- legacy flat layout, the reference encoder's 512-row segments (pure numpy, small cases) -----------------
+def encode_legacy_segments(plane, freqs, cdf, seg_rows=512):
+    """Stream g = seg * cols + col codes rows [seg * seg_rows, + seg_rows) of column col, last row first, so
+    that the decoder (comp_inference/rans_triton.py:171-241) meets them first row first; byte j of stream g
+    sits at j * num_streams + g and the decoder reads from sizes[g] - 1 downwards.  Encoder step as in
+    src/cuda/rans_kernels.cuh:393-509: renormalise while x >= ((L >> 12) << 8) * freq, then
+    x = (x // freq << 12) + x % freq + cdf.  Returns (stream u8, states u32, sizes u32)."""
+    p = _c(plane, np.uint8)
+    rows, cols = p.shape
+    f = np.asarray(freqs, np.uint64)
+    c = np.asarray(cdf, np.uint64)
+    segs = -(-rows // seg_rows)
+    S = segs * cols
+    x = np.full(S, 1 << 16, np.uint64)
+    emitted = [[] for _ in range(S)]
+    for i in range(seg_rows - 1, -1, -1):
+        for seg in range(segs):
+            r = seg * seg_rows + i
+            if r >= rows:
+                continue
+            for col in range(cols):
+                g = seg * cols + col
+                s = int(p[r, col])
+                fs, cs, xs = int(f[s]), int(c[s]), int(x[g])
+                lim = ((1 << 16) >> 12 << 8) * fs
+                while xs >= lim:
+                    emitted[g].append(xs & 0xFF)
+                    xs >>= 8
+                x[g] = ((xs // fs) << 12) + xs % fs + cs
+    sizes = np.array([len(e) for e in emitted], np.uint32)
+    stream = np.zeros(int(sizes.max(initial=0)) * S, np.uint8)
+    for g, e in enumerate(emitted):
+        if e:
+            stream[np.arange(len(e)) * S + g] = e
+    return stream, x.astype(np.uint32), sizes
+
+
+def decode_legacy_segments(stream, states, sizes, rows, cols, freqs, cdf, seg_rows=512):
+    """Inverse of encode_legacy_segments, following the reference's decoder loop
+    (comp_inference/rans_triton.py:199-241): symbol from the 12 low bits of the state, state update from the
+    symbol's frequency and cumulative count, at most two bytes per symbol while the state is below 2^16."""
+    t, slot_map = build_tables(freqs, cdf)
+    S = len(states)
+    out = np.zeros((rows, cols), np.uint8)
+    for g in range(S):
+        seg, col = divmod(g, cols)
+        x, off = int(states[g]), int(sizes[g]) - 1
+        for i in range(min(seg_rows, rows - seg * seg_rows)):
+            slot = x & 4095
+            s = int(slot_map[slot])
+            out[seg * seg_rows + i, col] = s
+            fs, cs = int(t[s]) & 0xFFFF, int(t[s]) >> 16
+            x = fs * (x >> 12) + slot - cs
+            for _ in range(2):
+                if x < (1 << 16) and off >= 0:
+                    x = (x << 8) | int(stream[off * S + g])
+                    off -= 1
+    return out

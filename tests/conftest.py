@@ -10,6 +10,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 GOLDEN = os.path.join(ROOT, "tests", "golden", "reference_vectors.npz")
+GOLDEN_LEGACY = os.path.join(ROOT, "tests", "golden", "reference_vectors_legacy.npz")
 
 
 def pytest_configure(config):
@@ -19,6 +20,12 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden():
     return np.load(GOLDEN)
+
+
+@pytest.fixture(scope="session")
+def golden_legacy():
+    """Legacy flat layout, streams the reference's rans_decomp_triton returned to the stored plane."""
+    return np.load(GOLDEN_LEGACY)
 
 
 @pytest.fixture(scope="session")

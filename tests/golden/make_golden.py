@@ -10,6 +10,9 @@ What comes from the reference itself (imported by file path, unmodified):
     uninterleave_mantissas       (comp_inference/comp_inference.py)
   * rans_decomp_triton_tiled     (comp_inference/rans_triton.py), Triton interpreter, CPU tensors
   * fused_rans_embedding_triton  (comp_inference/embedding_triton.py), same
+  * rans_decomp_triton           (comp_inference/rans_triton.py), the legacy flat layout in the stream order
+                                 of the reference's legacy encoder; written to reference_vectors_legacy.npz
+                                 (``--part legacy``)
 
 The reference's encoder is CUDA only and cannot run without a GPU, so the
 compressed streams stored here are produced by the CPU oracle; what pins them is
@@ -62,12 +65,59 @@ CASES = [
 
 LUT_CASES = 8
 
+LEGACY_CASES = [
+    # rows, cols, seed, std                  what it exercises
+    (1100, 24, 21, 0.02),                   # three segments, the last of 76 rows
+    (512, 40, 22, 0.02),                    # exactly one segment
+    (37, 130, 23, 1.0),                     # one short segment, more streams than one program of 128
+    (600, 8, 24, 0.0),                      # a single symbol: streams without bytes
+]
+
+
+def legacy_part(ref):
+    """The legacy flat layout: oracle-encoded streams that the reference's rans_decomp_triton returns to the
+    original plane bit for bit."""
+    rt, ci = ref["rans_triton"], ref["comp_inference"]
+    out = {}
+    for i, (rows, cols, seed, std) in enumerate(LEGACY_CASES):
+        g = torch.Generator().manual_seed(seed)
+        W = (torch.randn(rows, cols, generator=g) * std).to(torch.bfloat16)
+        e_ref, _ = ci.extract_exp_and_mantissa(W)
+        f_ref, c_ref = ci.get_rans_lut(e_ref)
+        stream, states, sizes = O.encode_legacy_segments(e_ref.numpy(), f_ref.numpy(), c_ref.numpy())
+        tables, slot_map = O.build_tables(f_ref.numpy().astype(np.uint16), c_ref.numpy().astype(np.uint16))
+        st = torch.from_numpy(stream if stream.size else np.zeros(1, np.uint8))
+        plane_ref = rt.rans_decomp_triton(
+            st, torch.from_numpy(states.view(np.int32).copy()),
+            torch.from_numpy(tables.view(np.int32).copy()), torch.from_numpy(slot_map.copy()),
+            torch.from_numpy(sizes.view(np.int32).copy()), (rows, cols))
+        assert torch.equal(plane_ref, e_ref), f"reference legacy decoder disagrees with the input plane, case {i}"
+        p = f"l{i}_"
+        out[p + "geom"] = np.array([rows, cols, seed], np.int64)
+        out[p + "exp"] = e_ref.numpy()
+        out[p + "freqs"] = f_ref.numpy().astype(np.uint16)
+        out[p + "cdf"] = c_ref.numpy().astype(np.uint16)
+        out[p + "stream"] = stream
+        out[p + "states"] = states
+        out[p + "sizes"] = sizes
+        out[p + "tables"] = tables
+        out[p + "slot_map"] = slot_map
+        print(f"legacy case {i}: {rows}x{cols} streams={len(states)} bytes={stream.size} ok")
+    out["n_cases"] = np.array([len(LEGACY_CASES)], np.int64)
+    np.savez_compressed(os.path.join(HERE, "reference_vectors_legacy.npz"), **out)
+    print("wrote", os.path.join(HERE, "reference_vectors_legacy.npz"))
+
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-root", required=True)
+    ap.add_argument("--part", choices=("tiled", "legacy", "all"), default="all")
     a = ap.parse_args()
     ref = load_reference(a.ref_root)
+    if a.part in ("legacy", "all"):
+        legacy_part(ref)
+    if a.part == "legacy":
+        return
     rt, et, ci = ref["rans_triton"], ref["embedding_triton"], ref["comp_inference"]
 
     out = {}

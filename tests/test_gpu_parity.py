@@ -502,6 +502,32 @@ def test_rans_decomp_triton_round_trip(ci, rows, cols):
     assert out.dtype == torch.uint8 and torch.equal(out.cpu(), plane)
 
 
+@pytest.mark.parametrize("i", range(4))
+def test_legacy_segments_against_reference_vectors(ci, golden_legacy, i):
+    """Streams that the reference's own rans_decomp_triton returned to the stored plane (generated on the CPU
+    under the Triton interpreter): this library decodes them to the same plane, and its encoder writes the
+    same bytes, states and sizes."""
+    g = golden_legacy
+    p = f"l{i}_"
+    rows, cols = int(g[p + "geom"][0]), int(g[p + "geom"][1])
+    plane = torch.from_numpy(g[p + "exp"])
+
+    def dev32(a):
+        return torch.from_numpy(a.view(np.int32).copy()).cuda()
+
+    out = ci.rans_decomp_triton(torch.from_numpy(g[p + "stream"]).cuda(), dev32(g[p + "states"]),
+                                dev32(g[p + "tables"]), torch.from_numpy(g[p + "slot_map"]).cuda(),
+                                dev32(g[p + "sizes"]), (rows, cols))
+    assert torch.equal(out.cpu(), plane)
+    r = ci.ccore.RansManager(plane.numel()).compress_segments(plane, g[p + "freqs"], g[p + "cdf"])
+    assert r.success and r.num_streams == len(g[p + "states"])
+    assert np.array_equal(r.states.numpy().view(np.uint32), g[p + "states"])
+    assert np.array_equal(r.sizes.numpy().view(np.uint32), g[p + "sizes"])
+    assert np.array_equal(r.stream.numpy(), g[p + "stream"])
+    assert np.array_equal(r.tables.numpy().view(np.uint32), g[p + "tables"])
+    assert np.array_equal(r.slot_map.numpy(), g[p + "slot_map"])
+
+
 # ------------------------------------------------------------------ errors find their way out
 
 def test_status_word_travels_through_the_abi(ci):
