@@ -341,6 +341,17 @@ def secondary_metrics(mods, dense, device, peak_hbm, peak_tf, src):
                                    "TFLOPs": flops_per_row * M / (ms * 1e-3) / 1e12,
                                    "kernel": "k_decode4 into a scratch buffer + cuBLAS bf16 GEMM"}
         prefill[f"M{M}"] = row
+    # both routes at batch sizes between the GEMV kernels' 16 rows and a prompt: why the modules' default is 17
+    small_rows = {}
+    for M in (32, 128):
+        x = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(2000 + M)).to(torch.bfloat16).to(device)
+        row = {}
+        for pol in ("fused", "decode_then_gemm"):
+            for m in mods.values():
+                m.prefill_policy = pol
+            row[pol + "_ms"] = timed(lambda: block_step(mods, x), 10)
+        small_rows[f"M{M}"] = row
+    out["prefill_rows_32_128"] = small_rows
     for m in mods.values():
         m.prefill_policy = "auto"
     out["prefill"] = dict(prefill, kernel="k_linear_gemm (tcgen05.mma, TMEM accumulators); 'auto' = the library's own split-K choice",
@@ -422,6 +433,7 @@ def full_model(rank, world, device, barrier):
         for B in (1, 8):
             if B == 1:
                 ref["all1"] = runner.prefill(ids[:1], all_logits=True)[0].float()
+            runner.prefill(ids[:B])                             # untimed: first-use allocations, library plans
             toks, first, t = runner.generate(ids[:B], NEW)
             ref[f"toks{B}"], ref[f"first{B}"], ref[f"t{B}"] = toks.cpu(), first.float().cpu(), t
         runner.release()
@@ -465,7 +477,8 @@ def full_model(rank, world, device, barrier):
            "compressed_GB": comp_bytes / 1e9, "modules": kinds,
            "parallelism": "single GPU" if world == 1 else f"tp{world}: column/row shards, vocabulary-parallel LM head",
            "decode": "one CUDA graph replay per token (embedding gather, 32 layers, LM head, argmax, KV update)",
-           "prefill": "module default: stand-alone decode + library GEMM from 256 rows up (prefill_policy='auto')",
+           "prefill": "module default: stand-alone decode + library GEMM above 16 rows (prefill_policy='auto'); one "
+                      "untimed prompt pass per batch size comes first (first-use allocations, library plan selection)",
            "parity_note": "weights are bit-identical to the dense model's; a random-init model has near-tied logits, "
                           "so free-running greedy sequences part at the first near-tie.  near_best = share of "
                           "generated tokens whose dense-bf16 logit (dense model teacher-forced on that sequence) is "
@@ -477,6 +490,7 @@ def full_model(rank, world, device, barrier):
 
     for B in (1, 8):
         mine_all = runner.prefill(ids[:1], all_logits=True)[0].float() if B == 1 else None
+        runner.prefill(ids[:B])                                 # untimed, as for the dense model
         toks, first, t = runner.generate(ids[:B], NEW, barrier=barrier)
         row = {"prefill_tok_s": t["prefill_tok_s"], "decode_tok_s": t["decode_tok_s"],
                "decode_ms_per_token": 1e3 * t["decode_s"] / (NEW - 1), "prefill_s": t["prefill_s"]}

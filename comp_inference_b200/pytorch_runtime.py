@@ -77,31 +77,52 @@ class _RansBase(nn.Module):
 
 
 _scratch = {}
+_scratch_retired = []
 
 
 def _decode_scratch(device, K, N):
-    """One bf16 buffer per device, grown on demand, that the decode-then-GEMM prefill path decodes into."""
-    buf = _scratch.get(device)
+    """The bf16 buffer the decode-then-GEMM route decodes into: one per (device, stream) -- two streams may run
+    this route at the same time -- grown on demand.  A buffer that is outgrown is kept alive, not freed: a
+    captured graph may still write to it."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
     if buf is None or buf.numel() < K * N:
+        if buf is not None:
+            _scratch_retired.append(buf)
         buf = torch.empty(K * N, dtype=torch.bfloat16, device=device)
-        _scratch[device] = buf
+        _scratch[key] = buf
     return buf[:K * N].view(K, N)
+
+
+def _decode_then_gemm(w_desc, K, N, x2, bias=None, transposed=False):
+    """x2 [M, K] times the compressed weight behind ``w_desc``: one stand-alone decode into the device's scratch
+    buffer, then a library GEMM.  ``transposed``: the weight is stored [N, K] (the LM head's stored layout) and
+    the GEMM reads it as its transpose."""
+    rows, cols = (N, K) if transposed else (K, N)
+    w = _decode_scratch(x2.device, rows, cols)
+    _lib.check(_lib.load().ci_decode_bf16(w_desc, _lib.ptr(w), _lib.stream()))
+    y = torch.matmul(x2, w.t() if transposed else w)
+    if bias is not None:
+        y += bias
+    return y
 
 
 class RansLinear(_RansBase):
     """nn.Linear replacement; weight stored compressed as [K=in, N=out] (pytorch_runtime.py:397-459).
 
-    ``prefill_policy`` chooses what a call with many activation rows runs:
+    ``prefill_policy`` chooses what a call with more than 16 activation rows runs (up to 16 rows every policy
+    runs the fused decode-GEMV kernels):
     "fused" the decode-GEMM kernel at every size (tcgen05, the decoded weight never leaves the chip);
     "decode_then_gemm" / "auto" (default) from ``prefill_rows`` rows up the stand-alone decoder into a reused
     per-device scratch buffer followed by a library GEMM -- the reference's decompress + triton_matmul pair
     (comp_inference/triton_gemm.py:324-337): the weight is decoded once however many rows there are, at the full
-    rate of the stand-alone decoder, which on a B200 is 1.8x (512 rows) to 2.8x (2048 rows) faster than the fused
-    kernel; below ``prefill_rows`` rows both run the fused kernels.
+    rate of the stand-alone decoder.  Measured on a B200 over one Llama-2-7B block this route is the faster one
+    at every row count above 16 (0.31 ms against 0.50 ms at 17 rows, 0.32 / 0.53 at 128, 0.38 / 0.70 at 512,
+    0.50 / 1.24 at 1024), hence the default ``prefill_rows`` = 17.
     """
 
     def __init__(self, in_features: int, out_features: int, tile_k: int = 1024, tile_n: int = 32, split_k: int = 1,
-                 has_bias: bool = False, prefill_policy: str = "auto", prefill_rows: int = 256):
+                 has_bias: bool = False, prefill_policy: str = "auto", prefill_rows: int = 17):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.tile_k, self.tile_n, self.split_k = tile_k, tile_n, split_k
@@ -120,13 +141,8 @@ class RansLinear(_RansBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         K, N = self.in_features, self.out_features
         x2 = ops._check_x(x, K)
-        if self.prefill_policy != "fused" and x2.shape[0] >= self.prefill_rows:
-            w = _decode_scratch(x2.device, K, N)
-            _lib.check(_lib.load().ci_decode_bf16(self._weight(K, N), _lib.ptr(w), _lib.stream()))
-            y = torch.matmul(x2, w)
-            if self.bias is not None:
-                y += self.bias
-            return y.view(*x.shape[:-1], N)
+        if self.prefill_policy != "fused" and x2.shape[0] >= max(self.prefill_rows, 17):
+            return _decode_then_gemm(self._weight(K, N), K, N, x2, self.bias).view(*x.shape[:-1], N)
         y = ops._linear_call(self._weight(K, N), x2, x2.shape[0], N, self.bias, None,
                              self.split_k if self.split_k > 1 else 0, False)
         return y.view(*x.shape[:-1], N)
@@ -182,11 +198,12 @@ class RansLMHead(_RansBase):
     """
 
     def __init__(self, in_features: int, out_features: int, tile_k: int = 1024, tile_n: int = 32,
-                 fast_twin: bool = True, twin_tile=(128, 32)):
+                 fast_twin: bool = True, twin_tile=(128, 32), prefill_policy: str = "auto", prefill_rows: int = 17):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.tile_k, self.tile_n = tile_k, tile_n
         self.fast_twin, self.twin_tile = bool(fast_twin), (int(twin_tile[0]), int(twin_tile[1]))
+        self.prefill_policy, self.prefill_rows = prefill_policy, int(prefill_rows)   # as in RansLinear
         self._register()
 
     _twin = None
@@ -224,7 +241,12 @@ class RansLMHead(_RansBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         V, H = self.out_features, self.in_features
         x2 = ops._check_x(x, H)
-        if self.fast_twin:
+        if self.prefill_policy != "fused" and x2.shape[0] >= max(self.prefill_rows, 17):   # logits of a whole prompt
+            if self.fast_twin:
+                y = _decode_then_gemm(self._twin_weight(), H, V, x2)
+            else:
+                y = _decode_then_gemm(self._weight(V, H), H, V, x2, transposed=True)
+        elif self.fast_twin:
             y = ops._linear_call(self._twin_weight(), x2, x2.shape[0], V, None, None, 0, False)
         else:
             y = ops._linear_call(self._weight(V, H), x2, x2.shape[0], V, None, None, 0, True)
@@ -504,7 +526,10 @@ class RansVocabParallelLMHead(nn.Module):
         H, V = self.in_features, self.out_features
         x2 = ops._check_x(x, H)
         M = x2.shape[0]
-        y = ops._linear_call(self._w, x2, M, self.per_rank, None, None, 0, False)
+        if M >= 17:                                             # a whole prompt: decode once, library GEMM
+            y = _decode_then_gemm(self._w, H, self.per_rank, x2)
+        else:
+            y = ops._linear_call(self._w, x2, M, self.per_rank, None, None, 0, False)
         if self.gather is not None:
             full = self.gather(y)
         else:

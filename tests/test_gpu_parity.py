@@ -327,8 +327,23 @@ def test_prefill_policies_agree(ci):
         lin.bias = bias
         assert rel_err(lin(x).float().cpu().numpy(), ref) <= REL_TOL, policy
         assert rel_err(lin(x[:3]).float().cpu().numpy(), ref[:3]) <= REL_TOL, policy      # few rows: always fused
+        assert rel_err(lin(x[:17]).float().cpu().numpy(), ref[:17]) <= REL_TOL, policy    # the first row count of the library route
     with pytest.raises(ValueError):
         ci.RansLinear(K, N, 128, 32, prefill_policy="other")
+    # the scratch the library route decodes into is per stream and survives growth (a captured graph may hold it)
+    from comp_inference_b200 import pytorch_runtime as rt
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        y_side = lin(x)
+    side.synchronize()
+    assert rel_err(y_side.float().cpu().numpy(), ref) <= REL_TOL
+    dev_ = x.device
+    assert (dev_, side.cuda_stream) in rt._scratch and (dev_, torch.cuda.current_stream().cuda_stream) in rt._scratch
+    small = rt._decode_scratch(dev_, 8, 8)
+    base = small.data_ptr()
+    rt._decode_scratch(dev_, 4096, 4096)                        # grows: the old buffer is retired, not freed
+    assert any(b.data_ptr() == base for b in rt._scratch_retired) or rt._decode_scratch(dev_, 8, 8).data_ptr() == base
 
 
 def test_lm_head_twin_and_single_copy_modes(ci):
@@ -338,11 +353,13 @@ def test_lm_head_twin_and_single_copy_modes(ci):
     c = ci.compress_weight_cuda(W.cuda(), 128, 32)
     twin = ci.RansLMHead(H, V, 128, 32).load_compressed(c)
     single = ci.RansLMHead(H, V, 128, 32, fast_twin=False).load_compressed(c)
-    for M in (1, 3, 16):
+    fused = ci.RansLMHead(H, V, 128, 32, prefill_policy="fused").load_compressed(c)
+    for M in (1, 3, 16, 17, 200):                               # above 16 rows: decode once + library GEMM by default
         x = torch.randn(M, H, generator=torch.Generator().manual_seed(5 + M)).to(torch.bfloat16).cuda()
         ref = (x.double().cpu() @ W.double().t()).numpy()
         assert rel_err(twin(x).float().cpu().numpy(), ref) <= REL_TOL
         assert rel_err(single(x).float().cpu().numpy(), ref) <= REL_TOL
+        assert rel_err(fused(x).float().cpu().numpy(), ref) <= REL_TOL
     t = twin._twin[3]
     back = ci.rans_decompress_bf16(t["rans_exp_stream"], t["rans_exp_states"], t["rans_exp_tables"],
                                    t["rans_exp_slot_map"], (H, V), t["rans_exp_tile_offsets"],
