@@ -639,6 +639,60 @@ def kernels_once(args):
                       "gemm_rel_err": float((y512.float() - ref512).abs().max() / ref512.abs().max())}))
 
 
+def shards_once(args):
+    """Rank 0's four shard launches of an N-way tensor-parallel block on ONE GPU, no exchange: what a rank of
+    `--gpus N` runs between its exchanges.  A multi-rank command is never profiled; this single-process replay is
+    the case the per-launch figures and ncu captures of the shard kernels are taken on.  Three eager steps at
+    batch 1, the outputs checked against a dense product; with --shards-time also per-launch times (CUDA graphs of
+    eight launches each, weights L2 resident for the small shards)."""
+    import comp_inference_b200 as ci
+    from comp_inference_b200 import sharding, _lib
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    world = args.shards_once
+    mods, dense = {}, {}
+    for name, members, kind in LAYERS:
+        parts = [WEIGHTS[m][1] for m in members]
+        K = WEIGHTS[members[0]][0]
+        Wkn = make_fused_kn(members).to(dev)
+        if kind == "col":
+            c = sharding.shard_cols(ci.compress_weight_cuda(Wkn, TILE_H, TILE_W), 0, world, parts)
+            w = sum(parts) // world
+            dense[name] = torch.cat([Wkn[:, sum(parts[:i]):sum(parts[:i]) + p // world] for i, p in enumerate(parts)], 1)
+        elif sharding.can_shard_rows(K, TILE_H, world):
+            c = sharding.shard_rows(ci.compress_weight_cuda(Wkn, TILE_H, TILE_W), 0, world)
+            dense[name] = Wkn[:K // world]
+        else:
+            c = ci.compress_weight_cuda(Wkn[:K // world].contiguous(), TILE_H, TILE_W)
+            dense[name] = Wkn[:K // world]
+        del Wkn
+        k, n = c["shape"]
+        m = ci.RansLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(dev)
+        m.first_part = parts[0] // world
+        mods[name] = m.prepare()
+    res = {"shards_once": world, "layers": {}}
+    for name, m in mods.items():
+        x = torch.randn(1, m.in_features, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
+        for _ in range(3):
+            y = m(x)
+        torch.cuda.synchronize()
+        ref = x.float() @ dense[name].float()
+        row = {"shape_in_out": [m.in_features, m.out_features],
+               "kernel": ROUTES[_lib.load().ci_linear_route(m._weight(m.in_features, m.out_features), 1)],
+               "rel_err": float((y.float() - ref).abs().max() / ref.abs().max())}
+        if args.shards_time:
+            def many():
+                for _ in range(8):
+                    m(x)
+            row["us"] = timed(graphed(many).replay, 100, warm=10) * 1e3 / 8
+        res["layers"][name] = row
+    if args.shards_time:
+        x = torch.randn(1, HIDDEN, generator=torch.Generator().manual_seed(12)).to(torch.bfloat16).to(dev)
+        res["step_us"] = timed(graphed(lambda: block_step(mods, x)).replay, 200, warm=20) * 1e3
+    ci.check_status()
+    print(json.dumps(res))
+
+
 def cpu_baseline_run(M, steps, warmup):
     """Decode + matmul of the same block with the CPU oracle on all host cores; returns (tok/s, ms/step, cores)."""
     from oracle import oracle as O
@@ -958,6 +1012,10 @@ def main():
                     help="N > 1: all-reduce with the one-shot kernel behind the row-parallel GEMV instead of inside it")
     ap.add_argument("--reference-triton", action="store_true",
                     help="time the reference's own Triton fused linear from baseline/_ref (if installed) and exit")
+    ap.add_argument("--shards-once", type=int, default=0, metavar="N",
+                    help="one GPU: rank 0's four shard launches of an N-way tensor-parallel block, checked against a "
+                         "dense product (the case the shard kernels are profiled on)")
+    ap.add_argument("--shards-time", action="store_true", help="with --shards-once: per-launch and per-step times")
     ap.add_argument("--kernels-once", action="store_true",
                     help="run each hot kernel three times on one 4096x4096 weight and exit (the ncu capture case)")
     args = ap.parse_args()
@@ -965,6 +1023,8 @@ def main():
         reference_triton(args)
     elif args.kernels_once:
         kernels_once(args)
+    elif args.shards_once:
+        shards_once(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -46,7 +46,7 @@ struct Mma4Args {
     uint32_t stage_bytes;  // window + 128 initial states
     uint32_t per_warp;     // units per warp
     uint32_t total;        // units in the matrix
-    uint32_t pairs_k;      // tile-row pairs = tiles_k / 2
+    uint32_t pairs_k;      // tile-row pairs = ceil(tiles_k / 2)
     uint32_t y_vec;        // outputs can be written as 16-byte rows of eight
     uint32_t *status;      // set non-zero if a wait ran out
 };
@@ -104,10 +104,12 @@ __device__ __forceinline__ void renorm4(uint32_t &s0, uint32_t &s1, uint32_t &s2
 // a second pair of mma takes activation row g + 8 (xf[2], xf[3]).  Compared with the weights as the B
 // operand (one mma per column) this halves the mma count and the accumulators for up to 8 rows and needs
 // no interleaving of the activation registers.
-template <bool HI>
+// MASKED: the packed weights are and-ed with `mask` (all ones or zero) -- rows beyond K in the last unit of a
+// column group, where a lane still executes the warp-wide decode step but must contribute nothing.
+template <bool HI, bool MASKED = false>
 __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_t &s1, uint32_t &s2, uint32_t &s3,
                                        uint32_t &p0, uint32_t &p1, uint32_t &p2, uint32_t &p3, uint32_t lut_s,
-                                       const uint32_t (&m)[4], const uint32_t (&xf)[4]) {
+                                       const uint32_t (&m)[4], const uint32_t (&xf)[4], uint32_t mask = 0xFFFFFFFFu) {
     uint32_t b[4][2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {                               // two rows -> one packed pair per column
@@ -131,8 +133,15 @@ __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_
         b[2][h] = weight_pair4<2>(e2, f2, m[2 * h], m[2 * h + 1]);
         b[3][h] = weight_pair4<3>(e3, f3, m[2 * h], m[2 * h + 1]);
     }
-    const uint32_t w01[4] = {b[0][0], b[1][0], b[0][1], b[1][1]};
-    const uint32_t w23[4] = {b[2][0], b[3][0], b[2][1], b[3][1]};
+    uint32_t w01[4] = {b[0][0], b[1][0], b[0][1], b[1][1]};
+    uint32_t w23[4] = {b[2][0], b[3][0], b[2][1], b[3][1]};
+    if constexpr (MASKED) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            w01[i] &= mask;
+            w23[i] &= mask;
+        }
+    }
     mma_bf16(acc[0], w01, xf[0], xf[1]);
     mma_bf16(acc[1], w23, xf[0], xf[1]);
     if constexpr (HI) {
@@ -141,7 +150,9 @@ __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_
     }
 }
 
-template <bool HI>
+// RAGGED: K is not a whole number of tile pairs (an instantiation of its own, so that the common case carries
+// none of the bookkeeping below in its registers).
+template <bool HI, bool RAGGED>
 __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid_constant__ Mma4Args p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const LinArgs &a = p.a;
@@ -413,6 +424,7 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
     uint32_t cur_grp = lo / p.pairs_k;
     zero_acc();
     const uint32_t n_groups = g.half / 4;                       // 4-symbol groups per stream (even)
+    const uint32_t ragged_pk = (g.K % (2 * g.th)) ? p.pairs_k - 1 : 0xFFFFFFFFu;   // the unit index with rows beyond K
 
     uint32_t s0, s1, s2, s3, pos0, pos1, pos2, pos3;
     // Four symbols of each of the lane's streams -> four B fragments -> four mma.  m = sign+mantissa words
@@ -440,13 +452,34 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             zero_acc();
             cur_grp = grp;
         }
+        // The last unit of a column group is ragged when K is not a whole number of tile pairs: its lower tile
+        // may be missing, either tile may be short.  There a lane's segment holds n_my < n_groups 4-row groups
+        // (none at all for a missing tile); the lane keeps executing the warp-wide decode step on whatever its
+        // cursors find (reads stay inside shared memory, see the launcher) with its weights masked to zero, and
+        // reads activations and sign+mantissa bytes from addresses that exist.
+        const bool ragged = RAGGED && pk == ragged_pk;          // warp-uniform
+        uint32_t n_my = n_groups, tile_m = 2 * pk + tsel;
+        if (RAGGED && ragged) {
+            const uint32_t r0 = tile_m * g.th;
+            const uint32_t rows_t = r0 < g.K ? min(g.th, g.K - r0) : 0u;
+            const uint32_t seg = rows_t > hsel * g.half ? min(g.half, rows_t - hsel * g.half) : 0u;
+            n_my = seg >> 2;
+            if (rows_t == 0) tile_m = 2 * pk;                   // no such tile: the upper tile's bytes stand in
+        }
         // (row 0 of this lane's segment, its four columns) of the sign+mantissa plane, and its activations
         const uint32_t krow = (2 * pk + tsel) * g.th + hsel * g.half;
-        const uint8_t *mp = a.mantissa + ((size_t)(2 * pk + tsel) * g.tiles_n + grp) * (2 * seg_bytes) +
-                            hsel * seg_bytes + gq * 4;
+        const uint8_t *mp = a.mantissa + ((size_t)tile_m * g.tiles_n + grp) * (2 * seg_bytes) + hsel * seg_bytes + gq * 4;
         const uint16_t *xp0 = x0 + krow + 0, *xp1 = x1 + krow;
         uint32_t mA[4], xA[4], mB[4], xB[4];
-        fetch(mp, xp0, xp1, mA, xA);                            // in flight while the copies are awaited
+        // group j of a ragged unit: operands from where they exist, and the mask for its weights
+        auto fetch_at = [&](uint32_t j, uint32_t (&m)[4], uint32_t (&xf)[4]) -> uint32_t {
+            const bool live = j < n_my;
+            fetch(mp + j * 128, live ? xp0 + 4 * j : x0, live ? xp1 + 4 * j : x1, m, xf);
+            return live ? 0xFFFFFFFFu : 0u;
+        };
+        uint32_t mkA = 0xFFFFFFFFu;
+        if (!RAGGED || !ragged) fetch(mp, xp0, xp1, mA, xA);    // in flight while the copies are awaited
+        else mkA = fetch_at(0, mA, xA);
 
         const uint32_t ml = tsel ? nx_ml1 : nx_ml0;
         __syncwarp();                                           // every lane is done with the other stage
@@ -492,15 +525,27 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
         s2 = lds_u32(st_s + 8);
         s3 = lds_u32(st_s + 12);
 
+        if (!RAGGED || !ragged) {
 #pragma unroll 1
-        for (uint32_t gi = 0; gi < n_groups; gi += 2) {         // operands are fetched one group ahead
-            fetch(mp + 128, xp0 + 4, xp1 + 4, mB, xB);
-            group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
-            mp += 256;
-            xp0 += 8;
-            xp1 += 8;
-            if (gi + 2 < n_groups) fetch(mp, xp0, xp1, mA, xA);
-            group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
+            for (uint32_t gi = 0; gi < n_groups; gi += 2) {     // operands are fetched one group ahead
+                fetch(mp + 128, xp0 + 4, xp1 + 4, mB, xB);
+                group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
+                mp += 256;
+                xp0 += 8;
+                xp1 += 8;
+                if (gi + 2 < n_groups) fetch(mp, xp0, xp1, mA, xA);
+                group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
+            }
+        } else {
+            // as many groups as the longest segment of the warp has (n_groups is even)
+            const uint32_t n_run = (__reduce_max_sync(kFull, n_my) + 1u) & ~1u;
+#pragma unroll 1
+            for (uint32_t gi = 0; gi < n_run; gi += 2) {
+                const uint32_t mkB = fetch_at(gi + 1, mB, xB);
+                group4<HI, true>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA, mkA);
+                if (gi + 2 < n_run) mkA = fetch_at(gi + 2, mA, xA);
+                group4<HI, true>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB, mkB);
+            }
         }
         stage ^= 1;
     }
@@ -511,8 +556,9 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 
 int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     const Geom &g = a.g;
-    // whole tiles only, an even number of tile rows (a unit is a pair), 16-symbol-aligned streams
-    if (g.tw != 32 || g.th % 16 != 0 || g.K % (2 * g.th) != 0 || a.M > 16 || max_tile_len == 0) return 1;
+    // 16-symbol-aligned streams; K a multiple of 4 (a lane decodes and multiplies four rows at a time); the last
+    // pair of tile rows may lack its lower tile and either tile may be short
+    if (g.tw != 32 || g.th % 16 != 0 || g.K % 4 != 0 || a.M > 16 || max_tile_len == 0) return 1;
     if ((reinterpret_cast<uintptr_t>(a.stream) & 15u) || (reinterpret_cast<uintptr_t>(a.mantissa) & 15u) ||
         (reinterpret_cast<uintptr_t>(a.states) & 15u))
         return 1;
@@ -536,7 +582,7 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
 
     // Units per warp must be a whole number: pick the warp count whose grid wastes the least.
     const uint32_t P = (uint32_t)sm_count();
-    p.pairs_k = g.tiles_k / 2;
+    p.pairs_k = (g.tiles_k + 1) / 2;
     p.total = g.groups * p.pairs_k;
     // A unit here is a serial chain twice as long as in the two-streams kernel (two tiles instead of one).
     // That pays once the multiprocessors are saturated (about eight warps each); a small matrix -- a
@@ -562,9 +608,11 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     p.status = a.tickets + (kTicketBytes - 1);
     if (a.dry_run) return CI_OK;                                // qualification only
 
-    static SmemLimit lim_lo = {}, lim_hi = {};
-    if (int rc = ensure_smem_limit(lim_lo, (const void *)k_linear_mma4<false>, (size_t)max_smem)) return rc;
-    if (int rc = ensure_smem_limit(lim_hi, (const void *)k_linear_mma4<true>, (size_t)max_smem)) return rc;
+    const bool ragged = g.K % (2 * g.th) != 0;
+    void (*kernel)(Mma4Args) = a.M <= 8 ? (ragged ? k_linear_mma4<false, true> : k_linear_mma4<false, false>)
+                                        : (ragged ? k_linear_mma4<true, true> : k_linear_mma4<true, false>);
+    static SmemLimit lim[4] = {};
+    if (int rc = ensure_smem_limit(lim[(a.M > 8) * 2 + ragged], (const void *)kernel, (size_t)max_smem)) return rc;
     // Programmatic dependent launch: the grid may be scheduled while the previous kernel of the stream
     // drains; the kernel itself waits for that kernel before it reads activations or touches the workspace.
     cudaLaunchConfig_t cfg = {};
@@ -577,7 +625,7 @@ int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    CI_CUDA(cudaLaunchKernelEx(&cfg, a.M <= 8 ? k_linear_mma4<false> : k_linear_mma4<true>, p));
+    CI_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return CI_OK;
 }
 

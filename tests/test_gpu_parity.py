@@ -502,6 +502,31 @@ def test_fused_linear_wide_exponent_spread(ci, M):
     assert err <= REL_TOL, err
 
 
+@pytest.mark.parametrize("K,N", [(5504, 4096),      # 43 tile rows: the last pair has no lower tile
+                                 (2752, 4096),      # 21.5 tile rows: the last pair's lower tile holds 64 rows (no bottom half)
+                                 (1376, 8192),      # 10.75 tile rows: lower tile of 96 rows (bottom half of 32)
+                                 (416, 16384),      # 3.25 tile rows: lower tile of 32 rows (half a top half)
+                                 (276, 16384)])     # 2 tile rows + 20: a lone upper tile with five 4-row groups
+@pytest.mark.parametrize("M", [1, 2, 8, 16])
+def test_gemv_with_ragged_last_tile_pair(ci, K, N, M):
+    """K that is not a whole number of tile-row pairs (row shards of a tensor-parallel down projection, say) on the
+    four-streams kernel: rows beyond K contribute nothing, neighbouring memory is not read."""
+    from comp_inference_b200 import _lib
+    W = make_weight(K, N, seed=K + N).cuda()
+    c = ci.compress_weight_cuda(W, 128, 32)
+    a = _linear_args(c)
+    wd, keep = _lib.tiled_weight(a["compressed_data"], a["initial_states"], a["tables"], a["slot_map"], a["tile_offsets"],
+                                 a["tile_max_lens"], a["mantissas"], K, N, 128, 32, want_max=True)
+    assert _lib.load().ci_linear_route(wd, M) == 2              # k_linear_mma4
+    # the activations end exactly at the end of their allocation: a read beyond row K would leave it
+    x = torch.randn(M * K, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16).cuda().view(M, K)
+    y = ci.fused_rans_linear_triton(x, weight_shape=(K, N), SPLIT_K=0, **a)
+    ref = (x.float() @ W.float()).cpu().numpy()
+    assert rel_err(y.float().cpu().numpy(), ref) <= REL_TOL
+    assert allclose_frac(y.float().cpu().numpy(), ref) == 1.0
+    ci.check_status()
+
+
 # ------------------------------------------------------------------ legacy layout in the encoder's own stream order
 
 @pytest.mark.parametrize("rows,cols", [(1024, 64), (700, 33), (512, 1), (1500, 40)])
