@@ -104,12 +104,10 @@ __device__ __forceinline__ void renorm4(uint32_t &s0, uint32_t &s1, uint32_t &s2
 // a second pair of mma takes activation row g + 8 (xf[2], xf[3]).  Compared with the weights as the B
 // operand (one mma per column) this halves the mma count and the accumulators for up to 8 rows and needs
 // no interleaving of the activation registers.
-// MASKED: the packed weights are and-ed with `mask` (all ones or zero) -- rows beyond K in the last unit of a
-// column group, where a lane still executes the warp-wide decode step but must contribute nothing.
-template <bool HI, bool MASKED = false>
+template <bool HI>
 __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_t &s1, uint32_t &s2, uint32_t &s3,
                                        uint32_t &p0, uint32_t &p1, uint32_t &p2, uint32_t &p3, uint32_t lut_s,
-                                       const uint32_t (&m)[4], const uint32_t (&xf)[4], uint32_t mask = 0xFFFFFFFFu) {
+                                       const uint32_t (&m)[4], const uint32_t (&xf)[4]) {
     uint32_t b[4][2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {                               // two rows -> one packed pair per column
@@ -133,15 +131,8 @@ __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_
         b[2][h] = weight_pair4<2>(e2, f2, m[2 * h], m[2 * h + 1]);
         b[3][h] = weight_pair4<3>(e3, f3, m[2 * h], m[2 * h + 1]);
     }
-    uint32_t w01[4] = {b[0][0], b[1][0], b[0][1], b[1][1]};
-    uint32_t w23[4] = {b[2][0], b[3][0], b[2][1], b[3][1]};
-    if constexpr (MASKED) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            w01[i] &= mask;
-            w23[i] &= mask;
-        }
-    }
+    const uint32_t w01[4] = {b[0][0], b[1][0], b[0][1], b[1][1]};
+    const uint32_t w23[4] = {b[2][0], b[3][0], b[2][1], b[3][1]};
     mma_bf16(acc[0], w01, xf[0], xf[1]);
     mma_bf16(acc[1], w23, xf[0], xf[1]);
     if constexpr (HI) {
@@ -150,8 +141,13 @@ __device__ __forceinline__ void group4(float (&acc)[4][4], uint32_t &s0, uint32_
     }
 }
 
-// RAGGED: K is not a whole number of tile pairs (an instantiation of its own, so that the common case carries
-// none of the bookkeeping below in its registers).
+// RAGGED: K is not a whole number of tile pairs, so the last unit of a column group lacks its lower tile or ends
+// inside a tile (an instantiation of its own: the common case carries none of the bookkeeping in its registers).
+// Every lane still runs the full warp-wide loop.  A lane whose segment has n_my < n_groups 4-row groups reads
+// zeros instead of activations from group n_my on, and -- so that what it multiplies by those zeros stays a
+// finite number -- starts its stream over whenever it has used it up (a lane without a segment decodes the top
+// half of the upper tile, which always exists).  Its products are exact zeros.
+__device__ __align__(16) uint16_t g_zero_activations[256];     // 64 per unit are read, 8 more are prefetched
 template <bool HI, bool RAGGED>
 __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid_constant__ Mma4Args p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -452,36 +448,29 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
             zero_acc();
             cur_grp = grp;
         }
-        // The last unit of a column group is ragged when K is not a whole number of tile pairs: its lower tile
-        // may be missing, either tile may be short.  There a lane's segment holds n_my < n_groups 4-row groups
-        // (none at all for a missing tile); the lane keeps executing the warp-wide decode step on whatever its
-        // cursors find (reads stay inside shared memory, see the launcher) with its weights masked to zero, and
-        // reads activations and sign+mantissa bytes from addresses that exist.
-        const bool ragged = RAGGED && pk == ragged_pk;          // warp-uniform
-        uint32_t n_my = n_groups, tile_m = 2 * pk + tsel;
-        if (RAGGED && ragged) {
-            const uint32_t r0 = tile_m * g.th;
+        // Groups of this lane's segment that exist (n_my) and of the stream it decodes (len); see the kernel's header.
+        uint32_t n_my = n_groups, len = n_groups;
+        uint32_t tsel_d = tsel, hsel_d = hsel;                  // the segment whose stream and bytes this lane decodes
+        if (RAGGED && pk == ragged_pk) {
+            const uint32_t r0 = (2 * pk + tsel) * g.th;
             const uint32_t rows_t = r0 < g.K ? min(g.th, g.K - r0) : 0u;
             const uint32_t seg = rows_t > hsel * g.half ? min(g.half, rows_t - hsel * g.half) : 0u;
-            n_my = seg >> 2;
-            if (rows_t == 0) tile_m = 2 * pk;                   // no such tile: the upper tile's bytes stand in
+            n_my = len = seg >> 2;
+            if (seg == 0) {                                     // nothing of its own: the upper tile's top half stands in
+                tsel_d = hsel_d = 0;
+                len = min(g.half, g.K - 2 * pk * g.th) >> 2;
+            }
         }
         // (row 0 of this lane's segment, its four columns) of the sign+mantissa plane, and its activations
         const uint32_t krow = (2 * pk + tsel) * g.th + hsel * g.half;
-        const uint8_t *mp = a.mantissa + ((size_t)tile_m * g.tiles_n + grp) * (2 * seg_bytes) + hsel * seg_bytes + gq * 4;
+        const uint8_t *mp = a.mantissa + ((size_t)(2 * pk + tsel_d) * g.tiles_n + grp) * (2 * seg_bytes) +
+                            hsel_d * seg_bytes + gq * 4;
         const uint16_t *xp0 = x0 + krow + 0, *xp1 = x1 + krow;
+        if (RAGGED && n_my == 0) xp0 = xp1 = g_zero_activations;
         uint32_t mA[4], xA[4], mB[4], xB[4];
-        // group j of a ragged unit: operands from where they exist, and the mask for its weights
-        auto fetch_at = [&](uint32_t j, uint32_t (&m)[4], uint32_t (&xf)[4]) -> uint32_t {
-            const bool live = j < n_my;
-            fetch(mp + j * 128, live ? xp0 + 4 * j : x0, live ? xp1 + 4 * j : x1, m, xf);
-            return live ? 0xFFFFFFFFu : 0u;
-        };
-        uint32_t mkA = 0xFFFFFFFFu;
-        if (!RAGGED || !ragged) fetch(mp, xp0, xp1, mA, xA);    // in flight while the copies are awaited
-        else mkA = fetch_at(0, mA, xA);
+        fetch(mp, xp0, xp1, mA, xA);                            // in flight while the copies are awaited
 
-        const uint32_t ml = tsel ? nx_ml1 : nx_ml0;
+        const uint32_t ml = (RAGGED ? tsel_d : tsel) ? nx_ml1 : nx_ml0;
         __syncwarp();                                           // every lane is done with the other stage
         if (t + 1 < hi) {
             if (t + 1 - dbase == 32) {
@@ -498,9 +487,10 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 
         // ---- this lane's four streams --------------------------------------
         const uint32_t win_s = wbase_s + stage * p.stage_bytes;
-        const uint32_t st_s = win_s + st_off + tsel * 256 + (hsel * 32 + gq * 4) * 4;
-        pos0 = win_s + tsel * 64 + hsel * 32 + gq * 4;
+        const uint32_t st_s = win_s + st_off + (RAGGED ? tsel_d : tsel) * 256 + ((RAGGED ? hsel_d : hsel) * 32 + gq * 4) * 4;
+        pos0 = win_s + (RAGGED ? tsel_d : tsel) * 64 + (RAGGED ? hsel_d : hsel) * 32 + gq * 4;
         if (ml <= p.cap_rows) pos0 += (ml - 1) * 128;           // last byte row; an empty tile starts one row below
+        const uint32_t pos_first = pos0;
         pos1 = pos0 + 1;
         pos2 = pos0 + 2;
         pos3 = pos0 + 3;
@@ -525,26 +515,33 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
         s2 = lds_u32(st_s + 8);
         s3 = lds_u32(st_s + 12);
 
-        if (!RAGGED || !ragged) {
+        uint32_t left = len;                                    // groups until this lane's stream is used up (RAGGED)
 #pragma unroll 1
-            for (uint32_t gi = 0; gi < n_groups; gi += 2) {     // operands are fetched one group ahead
-                fetch(mp + 128, xp0 + 4, xp1 + 4, mB, xB);
-                group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
-                mp += 256;
-                xp0 += 8;
-                xp1 += 8;
-                if (gi + 2 < n_groups) fetch(mp, xp0, xp1, mA, xA);
-                group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
+        for (uint32_t gi = 0; gi < n_groups; gi += 2) {         // operands are fetched one group ahead
+            fetch(mp + 128, xp0 + 4, xp1 + 4, mB, xB);
+            group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA);
+            mp += 256;
+            xp0 += 8;
+            xp1 += 8;
+            if constexpr (RAGGED) {
+                if (gi + 2 == n_my) xp0 = xp1 = g_zero_activations;   // rows beyond K from the next group on
             }
-        } else {
-            // as many groups as the longest segment of the warp has (n_groups is even)
-            const uint32_t n_run = (__reduce_max_sync(kFull, n_my) + 1u) & ~1u;
-#pragma unroll 1
-            for (uint32_t gi = 0; gi < n_run; gi += 2) {
-                const uint32_t mkB = fetch_at(gi + 1, mB, xB);
-                group4<HI, true>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mA, xA, mkA);
-                if (gi + 2 < n_run) mkA = fetch_at(gi + 2, mA, xA);
-                group4<HI, true>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB, mkB);
+            if (gi + 2 < n_groups) fetch(mp, xp0, xp1, mA, xA);
+            group4<HI>(acc, s0, s1, s2, s3, pos0, pos1, pos2, pos3, lut_s, mB, xB);
+            if constexpr (RAGGED) {
+                left -= 2;
+                if (left == 0) {                                // stream used up: start it over (its products meet zeros)
+                    left = len;
+                    s0 = lds_u32(st_s);
+                    s1 = lds_u32(st_s + 4);
+                    s2 = lds_u32(st_s + 8);
+                    s3 = lds_u32(st_s + 12);
+                    pos0 = pos_first;
+                    pos1 = pos0 + 1;
+                    pos2 = pos0 + 2;
+                    pos3 = pos0 + 3;
+                    mp -= len * 128;                            // and its sign+mantissa rows with it
+                }
             }
         }
         stage ^= 1;
@@ -556,9 +553,9 @@ __global__ void __launch_bounds__(kMma4Warps * 32, 1) k_linear_mma4(const __grid
 
 int launch_linear_mma4(const LinArgs &a, uint32_t max_tile_len, cudaStream_t s) {
     const Geom &g = a.g;
-    // 16-symbol-aligned streams; K a multiple of 4 (a lane decodes and multiplies four rows at a time); the last
-    // pair of tile rows may lack its lower tile and either tile may be short
-    if (g.tw != 32 || g.th % 16 != 0 || g.K % 4 != 0 || a.M > 16 || max_tile_len == 0) return 1;
+    // 16-symbol-aligned streams; K a multiple of 8 (the loop decodes and multiplies two groups of four rows per
+    // pass); the last pair of tile rows may lack its lower tile and either tile may be short
+    if (g.tw != 32 || g.th % 16 != 0 || g.K % 8 != 0 || a.M > 16 || max_tile_len == 0) return 1;
     if ((reinterpret_cast<uintptr_t>(a.stream) & 15u) || (reinterpret_cast<uintptr_t>(a.mantissa) & 15u) ||
         (reinterpret_cast<uintptr_t>(a.states) & 15u))
         return 1;

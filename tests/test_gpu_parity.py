@@ -506,7 +506,8 @@ def test_fused_linear_wide_exponent_spread(ci, M):
                                  (2752, 4096),      # 21.5 tile rows: the last pair's lower tile holds 64 rows (no bottom half)
                                  (1376, 8192),      # 10.75 tile rows: lower tile of 96 rows (bottom half of 32)
                                  (416, 16384),      # 3.25 tile rows: lower tile of 32 rows (half a top half)
-                                 (276, 16384)])     # 2 tile rows + 20: a lone upper tile with five 4-row groups
+                                 (280, 16384),     # 2 tile rows + 24: a lone upper tile with six 4-row groups in its top half only
+                                 (264, 16384)])     # 2 tile rows + 8
 @pytest.mark.parametrize("M", [1, 2, 8, 16])
 def test_gemv_with_ragged_last_tile_pair(ci, K, N, M):
     """K that is not a whole number of tile-row pairs (row shards of a tensor-parallel down projection, say) on the
