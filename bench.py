@@ -161,6 +161,26 @@ def compressed_bytes(c):
                 "rans_man_raw")) + 1024 + 4096
 
 
+def clone_block(mods, device):
+    """A second set of modules with copies of the same compressed arrays at other addresses (for the rotation that
+    keeps a rank's weights out of L2 between steps)."""
+    import comp_inference_b200 as ci
+    out = {}
+    for name, m in mods.items():
+        c = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in m.bench_compressed.items()}
+        if hasattr(m, "reducer"):
+            new = ci.RansRowParallelLinear(m.in_features, m.out_features, m.tile_k, m.tile_n).load_compressed(c).to(device)
+        else:
+            new = ci.RansLinear(m.in_features, m.out_features, m.tile_k, m.tile_n).load_compressed(c).to(device)
+        new.first_part, new.bench_compressed = m.first_part, c
+        out[name] = new
+    return out
+
+
+def l2_bytes(device):
+    return int(getattr(torch.cuda.get_device_properties(device), "L2_cache_size", 0)) or 126 * 1024 * 1024
+
+
 def build_block(rank, world, device, keep_dense=False):
     """Compressed modules of this rank's part of the block, plus byte counts for the roofline."""
     import comp_inference_b200 as ci
@@ -191,6 +211,7 @@ def build_block(rank, world, device, keep_dense=False):
         else:
             m = ci.RansLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(device)
         m.first_part = parts[0] // world                        # width of the block that feeds the next layer
+        m.bench_compressed = c
         mods[name] = m
         wbytes += compressed_bytes(c)
     return mods, wbytes, notes, dense
@@ -644,13 +665,14 @@ def shards_once(args):
     `--gpus N` runs between its exchanges.  A multi-rank command is never profiled; this single-process replay is
     the case the per-launch figures and ncu captures of the shard kernels are taken on.  Three eager steps at
     batch 1, the outputs checked against a dense product; with --shards-time also per-launch times (CUDA graphs of
-    eight launches each, weights L2 resident for the small shards)."""
+    eight launches each, weights L2 resident for the small shards) and the step time over copies of the shards in
+    rotation (weights from HBM)."""
     import comp_inference_b200 as ci
     from comp_inference_b200 import sharding, _lib
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     world = args.shards_once
-    mods, dense = {}, {}
+    mods, dense, wbytes = {}, {}, 0
     for name, members, kind in LAYERS:
         parts = [WEIGHTS[m][1] for m in members]
         K = WEIGHTS[members[0]][0]
@@ -668,9 +690,10 @@ def shards_once(args):
         del Wkn
         k, n = c["shape"]
         m = ci.RansLinear(k, n, c["tile_height"], c["tile_width"]).load_compressed(c).to(dev)
-        m.first_part = parts[0] // world
+        m.first_part, m.bench_compressed = parts[0] // world, c
+        wbytes += compressed_bytes(c)
         mods[name] = m.prepare()
-    res = {"shards_once": world, "layers": {}}
+    res = {"shards_once": world, "tile": [TILE_H, TILE_W], "layers": {}}
     for name, m in mods.items():
         x = torch.randn(1, m.in_features, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
         for _ in range(3):
@@ -688,7 +711,19 @@ def shards_once(args):
         res["layers"][name] = row
     if args.shards_time:
         x = torch.randn(1, HIDDEN, generator=torch.Generator().manual_seed(12)).to(torch.bfloat16).to(dev)
-        res["step_us"] = timed(graphed(lambda: block_step(mods, x)).replay, 200, warm=20) * 1e3
+        res["step_us_l2_resident"] = timed(graphed(lambda: block_step(mods, x)).replay, 200, warm=20) * 1e3
+        # the step as a model with many layers sees it: copies of the shards in rotation, together larger than L2
+        copies = max(2, -(-int(1.25 * l2_bytes(dev)) // int(wbytes)))
+        sets = [mods] + [clone_block(mods, dev) for _ in range(copies - 1)]
+        for ms in sets[1:]:
+            for m in ms.values():
+                m.prepare()
+
+        def rotation():
+            for ms in sets:
+                block_step(ms, x)
+        res["copies"] = copies
+        res["step_us"] = timed(graphed(rotation).replay, 100, warm=10) * 1e3 / copies
     ci.check_status()
     print(json.dumps(res))
 
@@ -737,14 +772,19 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def workload_config(M, world):
+def workload_config(M, world, copies=1, rank_mb=290.0):
+    if copies == 1:
+        l2 = f"inputs larger than L2 (about {rank_mb:.0f} MB of compressed weights per GPU and step)"
+    else:
+        l2 = (f"inputs larger than L2: {copies} copies of the GPU's shards at different addresses, one per step in "
+              f"rotation ({copies} x {rank_mb:.0f} MB per GPU)")
     return {"workload": "llama2-7b decoder block, 7 compressed linears, fused decode-GEMV", "batch": M,
             "shapes_out_in": [[4096, 4096]] * 4 + [[11008, 4096]] * 2 + [[4096, 11008]],
             "launches_per_step": 4,
             "fused_projections": "q|k|v as one [4096,12288] and gate|up as one [4096,22016] compressed matrix "
                                  "(rans_compress_qkv_fused / rans_compress_gate_up_fused): 4 launches over the 7 weights",
             "tile": [TILE_H, TILE_W], "weights": "N(0,0.02) bf16, seeded", "activations": "N(0,1) bf16",
-            "l2": "inputs larger than L2 (about 290 MB of compressed weights per step)",
+            "l2": l2,
             "parallelism": "single GPU" if world == 1 else f"tp{world} (column/row shards of the compressed tiles)"}
 
 
@@ -766,11 +806,16 @@ def run_ours(args):
     M = args.batch
     peak_hbm, peak_tf, src = peaks()
     mods, wbytes, notes, dense = build_block(rank, world, device, keep_dense=(world == 1 and not args.no_extra))
+    # A rank's shards shrink with N; below about one L2 size they would stay cached from step to step.  Steps then
+    # rotate over several copies of the shards so that every step streams its weights from HBM, as a model with
+    # many layers does.
+    copies = max(1, -(-int(1.25 * l2_bytes(device)) // int(wbytes)))
+    sets = [mods] + [clone_block(mods, device) for _ in range(copies - 1)]
     reducer = None
     if world > 1:
         from comp_inference_b200.collective import OneShotAllReduce
         reducer = OneShotAllReduce(capacity=16 * HIDDEN, device=device)
-        row_mods = [m for m in mods.values() if hasattr(m, "reducer")]
+        row_mods = [m for ms in sets for m in ms.values() if hasattr(m, "reducer")]
         for m in row_mods:
             m.reducer = reducer
             m.fuse_exchange = not args.no_fuse_exchange
@@ -780,9 +825,10 @@ def run_ours(args):
                "one-shot kernel behind the GEMV" if not any(fused) else "fused in some layers, one-shot kernel in others")
         notes.append(f"activation all-reduce over peer memory, {how}" if reducer.native
                      else f"activation all-reduce: NCCL ({reducer.why})")
-    for m in mods.values():
-        if not hasattr(m, "reducer"):
-            m.prepare()
+    for ms in sets:
+        for m in ms.values():
+            if not hasattr(m, "reducer"):
+                m.prepare()
 
     gen = torch.Generator().manual_seed(2000 + M)
     x_host = torch.randn(M, HIDDEN, generator=gen).to(torch.bfloat16).pin_memory()
@@ -804,18 +850,28 @@ def run_ours(args):
 
     # ---- device-resident: one CUDA graph per step -------------------------------------------
     for _ in range(3):
-        block_step(mods, x_dev)
+        for ms in sets:
+            block_step(ms, x_dev)
     torch.cuda.synchronize()
     trace("eager warm-up done")
     side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
+    graphs, y_graph = [], None
     with torch.cuda.stream(side):
-        block_step(mods, x_dev)
-        torch.cuda.synchronize()
-        with torch.cuda.graph(graph, stream=side):
-            y_graph = block_step(mods, x_dev)
+        for ms in sets:
+            block_step(ms, x_dev)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                y = block_step(ms, x_dev)
+            graphs.append(g)
+            y_graph = y if y_graph is None else y_graph
     torch.cuda.synchronize()
-    trace("graph captured")
+    trace(f"{len(graphs)} graph(s) captured")
+    turn = [0]
+
+    def device_step():                                          # one step = one replay, the copies taking turns
+        graphs[turn[0] % len(graphs)].replay()
+        turn[0] += 1
 
     def barrier():
         if world > 1:
@@ -842,12 +898,12 @@ def run_ours(args):
         return out
 
     for _ in range(max(args.warmup, 3)):
-        graph.replay()
+        device_step()
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
         time.sleep(0.3)
-    dev_runs = timed_region(graph.replay)
+    dev_runs = timed_region(device_step)
     dev_ms = statistics.median(dev_runs)
     trace(f"device loop done {dev_ms:.4f} ms/step")
 
@@ -856,19 +912,24 @@ def run_ours(args):
     # module calls, copy of the result to pinned host memory) is captured once with torch.cuda.graph
     # and replayed; the caller waits for the result before the next token.
     x_in = torch.empty_like(x_dev)
-    e2e_graph = torch.cuda.CUDAGraph()
+    e2e_graphs, e2e_keep = [], []
     with torch.cuda.stream(side):
-        x_in.copy_(x_host, non_blocking=True)
-        y_host.copy_(block_step(mods, x_in), non_blocking=True)
-        torch.cuda.synchronize()
-        with torch.cuda.graph(e2e_graph, stream=side):
+        for ms in sets:
             x_in.copy_(x_host, non_blocking=True)
-            y_e2e = block_step(mods, x_in)
-            y_host.copy_(y_e2e, non_blocking=True)
+            y_host.copy_(block_step(ms, x_in), non_blocking=True)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                x_in.copy_(x_host, non_blocking=True)
+                y_e2e = block_step(ms, x_in)
+                y_host.copy_(y_e2e, non_blocking=True)
+            e2e_graphs.append(g)
+            e2e_keep.append(y_e2e)
     torch.cuda.synchronize()
 
     def e2e_step():
-        e2e_graph.replay()
+        e2e_graphs[turn[0] % len(e2e_graphs)].replay()
+        turn[0] += 1
         torch.cuda.current_stream().synchronize()              # the caller needs the result before the next token
 
     for _ in range(max(args.warmup, 3)):
@@ -901,10 +962,11 @@ def run_ours(args):
             trace("reference Triton leg done")
     del dense
     # the block's graphs refer to the group's communicators; drop them before the model run sets up its own
-    del graph, y_graph, e2e_graph, y_e2e
-    for m in mods.values():
-        m.reducer = None
-    del mods
+    del graphs, y_graph, e2e_graphs, e2e_keep, y_e2e
+    for ms in sets:
+        for m in ms.values():
+            m.reducer = None
+    del mods, sets
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
     if reducer is not None:
@@ -924,7 +986,7 @@ def run_ours(args):
                 "repeats": REPEATS, "ms_per_step_min_max": [min(dev_runs), max(dev_runs)],
                 "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "u8 rANS decode + bf16 x bf16 -> fp32 (mma.sync)",
-                "data": "synthetic", "config": workload_config(M, world),
+                "data": "synthetic", "config": workload_config(M, world, copies, wbytes / 1e6),
                 "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
                         "ms_per_step_min_max": [min(e2e_runs), max(e2e_runs)],
                         "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
@@ -1012,6 +1074,8 @@ def main():
                     help="N > 1: all-reduce with the one-shot kernel behind the row-parallel GEMV instead of inside it")
     ap.add_argument("--reference-triton", action="store_true",
                     help="time the reference's own Triton fused linear from baseline/_ref (if installed) and exit")
+    ap.add_argument("--tile-height", type=int, default=0,
+                    help="tile height of the compressed weights (default: 128 on one GPU, 64 for tensor-parallel shards)")
     ap.add_argument("--shards-once", type=int, default=0, metavar="N",
                     help="one GPU: rank 0's four shard launches of an N-way tensor-parallel block, checked against a "
                          "dense product (the case the shard kernels are profiled on)")
@@ -1019,6 +1083,12 @@ def main():
     ap.add_argument("--kernels-once", action="store_true",
                     help="run each hot kernel three times on one 4096x4096 weight and exit (the ncu capture case)")
     args = ap.parse_args()
+    # Tile height is a per-tensor parameter of the stored format.  One GPU: 128 rows (fewest bytes, longest
+    # streams).  Tensor-parallel shards are small enough for a launch to be bounded by the length of one stream,
+    # not by throughput, and finish sooner with 64-row tiles (measured per N with --shards-once N --shards-time).
+    global TILE_H
+    ways = args.shards_once or int(os.environ.get("WORLD_SIZE", "1"))
+    TILE_H = args.tile_height or (128 if ways == 1 else 64)
     if args.reference_triton:
         reference_triton(args)
     elif args.kernels_once:

@@ -549,19 +549,34 @@ def _state_to_compressed(state_dict, name, th, tw):
     return c
 
 
-def _shard(c, kind, rank, world, device, parts=None):
+def _retiled(c, device, tile_height):
+    """The same weight re-encoded with another tile height (decoded and encoded on the GPU, bit-exact)."""
+    from . import comp_inference as ci_mod
+    K, N = c["shape"]
+    g = {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in c.items()}
+    w = ops.rans_decompress_bf16(g["rans_exp_stream"], g["rans_exp_states"], g["rans_exp_tables"],
+                                 g["rans_exp_slot_map"], (K, N), g["rans_exp_tile_offsets"],
+                                 g["rans_exp_tile_max_lens"], c["tile_height"], c["tile_width"], g["rans_man_raw"])
+    return ci_mod.compress_weight_cuda(w, int(tile_height), c["tile_width"])
+
+
+def _shard(c, kind, rank, world, device, parts=None, retile=None):
     """This rank's shard of a compressed [K, N] weight.  Cut out of the compressed arrays when the cut falls
     on tile boundaries; otherwise (Llama-2's 11008 rows over 8 ranks = 10.75 tiles) the rank decodes the
     weight once on the GPU and re-encodes its slice.  ``parts``: block widths of a concatenated projection
-    (the rank takes its slice of every block)."""
+    (the rank takes its slice of every block).  ``retile``: tile height the shard is to have (re-encoded on the
+    GPU if the package has another)."""
     from . import sharding
     from . import comp_inference as ci_mod
     K, N = c["shape"]
     th, tw = c["tile_height"], c["tile_width"]
+    want = int(retile) if retile else th
     if kind == "col" and sharding.can_shard_cols(N, tw, world, parts):
-        return sharding.shard_cols(c, rank, world, parts)
+        sc = sharding.shard_cols(c, rank, world, parts)
+        return sc if want == th else _retiled(sc, device, want)
     if kind == "row" and sharding.can_shard_rows(K, th, world):
-        return sharding.shard_rows(c, rank, world)
+        sc = sharding.shard_rows(c, rank, world)
+        return sc if want == th else _retiled(sc, device, want)
     if (kind == "col" and any(p % world for p in (parts or [N]))) or (kind == "row" and K % world):
         raise ValueError(f"{K}x{N} cannot be split {kind}-wise over {world} ranks")
     g = {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in c.items()}
@@ -578,19 +593,24 @@ def _shard(c, kind, rank, world, device, parts=None):
     else:
         k = K // world
         part = w[rank * k:(rank + 1) * k]
-    return ci_mod.compress_weight_cuda(part.contiguous(), th, tw)
+    return ci_mod.compress_weight_cuda(part.contiguous(), want, tw)
 
 
 def patch_model_tensor_parallel(model, state_dict, rank, world, group=None, layer_configs=None, default_th=1024,
-                                default_tw=32, device=None, oneshot_rows=16, vocab_parallel=True):
+                                default_tw=32, device=None, oneshot_rows=16, vocab_parallel=True,
+                                shard_tile_height=None):
     """patch_model for one rank of a tensor-parallel group.  q/k/v/gate/up projections (separate or
     concatenated) are cut column-wise (each rank owns a slice of the heads / of the FFN width), o/down
     projections row-wise with an all-reduce of their outputs; the LM head is cut by vocabulary with an
     all-gather of the logits (``vocab_parallel``; a vocabulary that does not divide stays replicated); the
     embedding table (one row gather per token, no arithmetic to share) and every uncompressed parameter are
     replicated.  The attention and MLP modules of the model are left as they are: they take the number of heads
-    and the FFN width from the tensors they are handed.  Returns the model, moved to ``device`` and prepared
-    (prepare_model), i.e. ready for graph capture."""
+    and the FFN width from the tensors they are handed.  ``shard_tile_height``: re-encode every linear shard with
+    this tile height at load (on the GPU, bit-exact weights).  A shard's launch is bounded by the length of one
+    stream rather than by throughput once the matrix is small, so shards of a package written with tall tiles run
+    faster with 64-row tiles (measured on a B200, Llama-2-7B block: 2 GPUs 132 -> 121 us per step, 8 GPUs 53 -> 50);
+    None keeps the package's tiles.  Returns the model, moved to ``device`` and prepared (prepare_model), i.e.
+    ready for graph capture."""
     layer_configs = layer_configs or {}
     device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
     reducer = gather = None
@@ -611,7 +631,8 @@ def patch_model_tensor_parallel(model, state_dict, rank, world, group=None, laye
             continue
         th, tw = _tile_of(state_dict, layer_configs, name, default_th, default_tw)
         parts = _fused_parts(model, name, module, state_dict) if kind == "col" else None
-        c = _shard(_state_to_compressed(state_dict, name, th, tw), kind, rank, world, device, parts)
+        c = _shard(_state_to_compressed(state_dict, name, th, tw), kind, rank, world, device, parts,
+                   retile=shard_tile_height)
         k, n = c["shape"]
         has_bias = module.bias is not None and parts is None
         if parts is not None:

@@ -187,6 +187,37 @@ def _worlds():
     return [w for w in (2, 4, 8) if w <= n] or [2]
 
 
+@pytest.mark.parametrize("kind,K,N,parts,th", [("col", 256, 768, [256, 256, 256], 128), ("row", 1024, 256, None, 128),
+                                                ("row", 2752, 128, None, 128), ("col", 256, 512, None, 64)])
+def test_shards_cut_and_retiled_at_load(kind, K, N, parts, th):
+    """One rank's shard as the tensor-parallel loader makes it -- cut out of the compressed arrays, or decoded and
+    re-encoded where the cut misses the tile grid -- with and without a new tile height: always the rank's slice
+    of the dense weight, bit for bit."""
+    import comp_inference_b200 as ci
+    from comp_inference_b200 import pytorch_runtime as rt
+    world = 4
+    g = torch.Generator().manual_seed(K + N)
+    W = (torch.randn(K, N, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    c = ci.compress_weight_cuda(W, th, 32)
+    for rank in (0, world - 1):
+        if kind == "col":
+            cols, start = [], 0
+            for p in (parts or [N]):
+                cols.append(W[:, start + rank * (p // world):start + (rank + 1) * (p // world)])
+                start += p
+            want = torch.cat(cols, dim=1).contiguous()
+        else:
+            want = W[rank * (K // world):(rank + 1) * (K // world)].contiguous()
+        for retile in (None, 32, 64):
+            s = rt._shard(c, kind, rank, world, torch.device("cuda", 0), parts, retile=retile)
+            assert s["tile_height"] == (retile or th) and tuple(s["shape"]) == tuple(want.shape)
+            back = ci.rans_decompress_bf16(s["rans_exp_stream"].cuda(), s["rans_exp_states"].cuda(),
+                                           s["rans_exp_tables"].cuda(), s["rans_exp_slot_map"].cuda(), s["shape"],
+                                           s["rans_exp_tile_offsets"].cuda(), s["rans_exp_tile_max_lens"].cuda(),
+                                           s["tile_height"], s["tile_width"], s["rans_man_raw"].cuda())
+            assert torch.equal(back.view(torch.uint16), want.view(torch.uint16)), (kind, rank, retile)
+
+
 @pytest.mark.parametrize("world", _worlds())
 @pytest.mark.parametrize("fuse", [False, True])
 def test_tensor_parallel_logits(tmp_path, world, fuse):
