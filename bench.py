@@ -679,7 +679,6 @@ def shards_once(args):
         Wkn = make_fused_kn(members).to(dev)
         if kind == "col":
             c = sharding.shard_cols(ci.compress_weight_cuda(Wkn, TILE_H, TILE_W), 0, world, parts)
-            w = sum(parts) // world
             dense[name] = torch.cat([Wkn[:, sum(parts[:i]):sum(parts[:i]) + p // world] for i, p in enumerate(parts)], 1)
         elif sharding.can_shard_rows(K, TILE_H, world):
             c = sharding.shard_rows(ci.compress_weight_cuda(Wkn, TILE_H, TILE_W), 0, world)
